@@ -42,7 +42,12 @@ EXPORTS = [
     "atx_embed_rows_scaled", "atx_tanh_norm", "atx_unary_act", "atx_head_prepare", "atx_head_gemm", "atx_attn_window",
     "atx_attn_window_prefill", "atx_attn_window_prefill_supported",
     "atx_attn_window_decode", "atx_attn_window_decode_supported", "atx_attn_window_decode_workspace_bytes",
+    "atx_resid_norm_scaled", "atx_embed_rows_pair", "atx_token_shift", "atx_poly_norm_act",
+    "atx_attn_paged", "atx_attn_paged_prefill", "atx_attn_paged_decode",
+    "atx_moe_route", "atx_moe_tile_rows", "atx_moe_plan", "atx_moe_expert_gemm", "atx_moe_combine",
 ]
+ATTN_SOFTMAX = 0
+ATTN_SIGMOID = 1
 ACT_RELU2 = 0
 ACT_GELU_TANH = 1
 HEAD_DST_ROWS = 0
@@ -56,9 +61,18 @@ class HeadSeg(C.Structure):
     _fields_ = [("src_off", C.c_int), ("src_stride", C.c_int), ("heads", C.c_int), ("width", C.c_int),
                 ("norm_dims", C.c_int), ("rot_off", C.c_int), ("rot_dims", C.c_int),
                 ("dst_kind", C.c_int), ("dst_off", C.c_int), ("dst_stride", C.c_int),
-                ("mix", C.c_float), ("reserved", C.c_int),
+                ("mix", C.c_float), ("rot_half", C.c_int),
                 ("norm_w", C.c_void_p), ("rot", C.c_void_p), ("mix_src", C.c_void_p), ("save", C.c_void_p),
                 ("dst", C.c_void_p), ("dst_ld", C.c_longlong)]
+
+
+class AttnOpts(C.Structure):
+    """atx_attn_opts: the options of atx_attn_paged / _prefill / _decode (include/atx_b200.h)."""
+
+    _fields_ = [("scale", C.c_float), ("softcap", C.c_float), ("out_scale", C.c_float),
+                ("chunk", C.c_int), ("window", C.c_int), ("keep_first", C.c_int), ("sink", C.c_int),
+                ("weight", C.c_int), ("gate_elem", C.c_int),
+                ("slopes", C.c_void_p), ("sinks", C.c_void_p), ("bias", C.c_void_p)]
 
 
 def head_segs(*segs: "HeadSeg"):
@@ -158,6 +172,22 @@ def load() -> C.CDLL:
     lib.atx_attn_window_decode_workspace_bytes.restype = i64
     lib.atx_attn_window_decode.argtypes = [vp, vp, vp, i64, i64, vp, i32, vp, vp, vp, i64, vp, i64, vp, i64, i32, i32, i32,
                                            i32, i32, i32, i32, f32, f32, i32, i32, vp, vp, i32, f32, i32, i32, vp]
+    lib.atx_resid_norm_scaled.argtypes = [vp, vp, vp, vp, vp, vp, vp, i32, vp, i32, i32, f32, i32, vp, i64, i32, i32, vp]
+    lib.atx_embed_rows_pair.argtypes = [vp, vp, f32, vp, i32, i32, i32, vp, vp, vp, vp, vp, vp, vp, i32, i32, i32, i32, i32, vp]
+    lib.atx_token_shift.argtypes = [vp, vp, vp, vp, vp, vp, vp, vp, vp, i32, i32, i32, i32, vp]
+    lib.atx_poly_norm_act.argtypes = [vp, i64, vp, vp, i64, i32, i32, f32, i32, i32, vp]
+    po = C.POINTER(AttnOpts)
+    lib.atx_attn_paged.argtypes = [vp, vp, vp, i64, i64, vp, i32, vp, vp, vp, i64, vp, i64, i32, i32, i32, i32, i32, i32,
+                                   po, i32, i32, vp]
+    lib.atx_attn_paged_prefill.argtypes = [vp, vp, vp, i64, i64, vp, i32, vp, vp, vp, i32, i32, vp, i64, vp, i64, i32, i32,
+                                           i32, i32, i32, po, i32, i32, vp]
+    lib.atx_attn_paged_decode.argtypes = [vp, vp, vp, i64, i64, vp, i32, vp, vp, vp, i64, vp, i64, vp, i64, i32, i32, i32,
+                                          i32, i32, i32, i32, po, i32, i32, vp]
+    lib.atx_moe_route.argtypes = [vp, i64, vp, i32, i32, f32, vp, vp, i32, i32, vp]
+    lib.atx_moe_tile_rows.argtypes = []
+    lib.atx_moe_plan.argtypes = [vp, i32, i32, vp, vp, vp, vp, i32, vp]
+    lib.atx_moe_expert_gemm.argtypes = [vp, i64, vp, i32, i32, vp, i64, i64, vp, i64, i32, i32, i32, vp, vp, i32, i32, i32, vp]
+    lib.atx_moe_combine.argtypes = [vp, vp, i64, vp, vp, vp, vp, vp, i64, i32, i32, i32, i32, i32, i32, vp]
     for name in EXPORTS:  # fail at load time, not at first use, if the build is stale
         getattr(lib, name)
     _lib = lib

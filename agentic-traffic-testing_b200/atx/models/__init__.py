@@ -10,9 +10,9 @@ from typing import Optional
 
 
 def _entries():
-    from . import gopopel, safisun
+    from . import gopopel, safisun, zonidra
 
-    return {"safisun": safisun, "gopopel": gopopel}
+    return {"safisun": safisun, "gopopel": gopopel, "zonidra": zonidra}
 
 
 def _module(arch: str):

@@ -2,6 +2,9 @@
 rotation angles."""
 from __future__ import annotations
 
+import math
+from typing import List, Optional
+
 import torch
 
 from .. import _cabi
@@ -47,4 +50,29 @@ def rotation_table(base: float, dims: int, max_pos: int, device: torch.device) -
     i = torch.arange(dims // 2, dtype=torch.float64)
     ang = torch.arange(max_pos, dtype=torch.float64)[:, None] * torch.pow(torch.tensor(base, dtype=torch.float64),
                                                                           -2.0 * i / dims)[None, :]
+    return torch.cat((ang.cos(), ang.sin()), -1).to(torch.float32).contiguous().to(device)
+
+
+def wavelength_scaled_frequencies(base: float, dims: int, scaling: Optional[dict]) -> List[float]:
+    """f_i = base^(-2i/dims), i < dims/2, rescaled by wavelength l = 2 pi / f (`scaling` = factor, low, high, original; None:
+    as they are): f stays where l < original / high, becomes f / factor where l > original / low, and between the two is
+    (1 - s) f / factor + s f with s = (original / l - low) / (high - low). Float64 on the host."""
+    out = []
+    for i in range(dims // 2):
+        f = float(base) ** (-2.0 * i / dims)
+        if scaling:
+            factor, low, high, orig = (float(scaling[k]) for k in ("factor", "low", "high", "original"))
+            wl = 2.0 * math.pi / f
+            if wl > orig / low:
+                f = f / factor
+            elif wl >= orig / high:
+                s = (orig / wl - low) / (high - low)
+                f = (1.0 - s) * f / factor + s * f
+        out.append(f)
+    return out
+
+
+def rotation_table_for(freqs: List[float], max_pos: int, device: torch.device) -> torch.Tensor:
+    """[max_pos, 2 * len(freqs)] fp32: cos then sin of p * f_i for the given frequencies, evaluated in float64 on the host."""
+    ang = torch.arange(max_pos, dtype=torch.float64)[:, None] * torch.tensor(freqs, dtype=torch.float64)[None, :]
     return torch.cat((ang.cos(), ang.sin()), -1).to(torch.float32).contiguous().to(device)

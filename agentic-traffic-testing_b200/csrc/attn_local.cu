@@ -178,7 +178,8 @@ attn_local_kernel(const XT* __restrict__ q, const XT* __restrict__ k_cache, cons
                   const int* __restrict__ positions, const float* __restrict__ gate, long long ldg,
                   XT* __restrict__ out, long long ldo, int H, int G, int D, int Vd, int bs, float scale, float softcap,
                   int chunk, int sink, float out_scale, long long k_row, long long v_row, int window,
-                  const float* __restrict__ slopes, const float* __restrict__ sinks) {
+                  const float* __restrict__ slopes, const float* __restrict__ sinks, int keep_first, int sigmoid_w,
+                  const float* __restrict__ bias, int gate_elem) {
     extern __shared__ float sm[];
     pdl_launch_dependents();
     pdl_wait();
@@ -192,6 +193,7 @@ attn_local_kernel(const XT* __restrict__ q, const XT* __restrict__ k_cache, cons
     int lo = chunk > 0 ? (pos / chunk) * chunk : 0;
     if (window > 0) lo = max(lo, pos - window + 1);   // sliding window: the row itself and the window - 1 tokens before it
     const float slope = slopes ? slopes[h] : 0.f;
+    const float hb = bias ? bias[h] : 0.f;   // added to every score of the head
     float* sq = sm + warp * D;
     for (int d = lane; d < D; d += 32) sq[d] = ldx(q, (t * H + h) * D + d) * scale;
     __syncwarp();
@@ -203,11 +205,15 @@ attn_local_kernel(const XT* __restrict__ q, const XT* __restrict__ k_cache, cons
     float acc[NV];
 #pragma unroll
     for (int i = 0; i < NV; ++i) acc[i] = 0.f;
-    for (int k0 = lo; k0 <= pos; k0 += 32) {
+    // keys come in two ranges: the first positions that stay visible below the window's edge, then the window itself
+    const int kept_end = min(keep_first, lo);
+    for (int range = kept_end > 0 ? 0 : 1; range < 2; ++range) {
+    const int k_begin = range == 0 ? 0 : lo, k_last = range == 0 ? kept_end - 1 : pos;
+    for (int k0 = k_begin; k0 <= k_last; k0 += 32) {
         const int kp = k0 + lane;
         float sc = -INFINITY;
         long long vbase = 0;
-        if (kp <= pos) {
+        if (kp <= k_last) {
             const int blk = bt[kp / bs];
             const long long tokslot = (static_cast<long long>(blk) * G + g) * bs + (kp % bs);
             const XT* kr = k_cache + tokslot * k_row;
@@ -216,15 +222,21 @@ attn_local_kernel(const XT* __restrict__ q, const XT* __restrict__ k_cache, cons
             for (int d = 0; d < D; ++d) dot = fmaf(sq[d], ldx(kr, d), dot);
             sc = softcap > 0.f ? softcap * tanhf(dot / softcap) : dot;
             sc -= slope * static_cast<float>(pos - kp);   // penalty per unit of distance
+            sc += hb;
         }
-        const float mt = fmaxf(m, warp_max(sc));
-        const float corr = (m == -INFINITY) ? 0.f : expf(m - mt);
-        const float p = (kp <= pos) ? expf(sc - mt) : 0.f;
-        l = l * corr + warp_sum(p);
+        float p;
+        if (sigmoid_w) {   // every visible key weighs sigmoid(score) by itself: no maximum, no sum
+            p = (kp <= k_last) ? 1.f / (1.f + expf(-sc)) : 0.f;
+        } else {
+            const float mt = fmaxf(m, warp_max(sc));
+            const float corr = (m == -INFINITY) ? 0.f : expf(m - mt);
+            p = (kp <= k_last) ? expf(sc - mt) : 0.f;
+            l = l * corr + warp_sum(p);
 #pragma unroll
-        for (int i = 0; i < NV; ++i) acc[i] *= corr;
-        m = mt;
-        const int nk = min(32, pos - k0 + 1);
+            for (int i = 0; i < NV; ++i) acc[i] *= corr;
+            m = mt;
+        }
+        const int nk = min(32, k_last - k0 + 1);
         for (int j = 0; j < nk; ++j) {
             const float pj = __shfl_sync(0xffffffffu, p, j);
             const long long vb = __shfl_sync(0xffffffffu, vbase, j);
@@ -235,12 +247,16 @@ attn_local_kernel(const XT* __restrict__ q, const XT* __restrict__ k_cache, cons
             }
         }
     }
-    float gmul = out_scale / l;
-    if (gate) gmul *= 1.f / (1.f + expf(-gate[t * ldg + h]));
+    }
+    float gmul = sigmoid_w ? out_scale : out_scale / l;
+    if (gate && !gate_elem) gmul *= 1.f / (1.f + expf(-gate[t * ldg + h]));
 #pragma unroll
     for (int i = 0; i < NV; ++i) {
         const int d = lane + 32 * i;
-        if (d < Vd) stx(out, t * ldo + static_cast<long long>(h) * Vd + d, acc[i] * gmul);
+        if (d >= Vd) continue;
+        float v = acc[i] * gmul;
+        if (gate && gate_elem) v *= 1.f / (1.f + expf(-gate[t * ldg + static_cast<long long>(h) * Vd + d]));
+        stx(out, t * ldo + static_cast<long long>(h) * Vd + d, v);
     }
 }
 
@@ -284,7 +300,12 @@ constexpr int kTcRows = 64, kTcKeys = 64;
 // slope and sink, so K and V are read once for the whole group. Slices (gridDim.z) write unnormalised partial outputs
 // with their running maximum and sum to `ws` and attn_split_merge_kernel folds them; the sink counts in slice 0 only.
 // Rows are listed by tok_seq / positions (one entry per token) instead of (first row, rows, first position) triples.
-template <int D, int VD, bool DEC>
+//
+// SIG: every visible key weighs sigmoid(score + bias[h]) by itself (no running maximum, no sum, no division at the end;
+// slices of the decode form simply add up). keep_first: keys at positions below it stay visible under the window's lower
+// edge; they are walked as tiles of their own in front of the window's tiles, up to where the window's tiles begin.
+// gate_elem: the gate holds a number per output element ([., H * vd_real]) instead of one per head.
+template <int D, int VD, bool DEC, bool SIG>
 __global__ void __launch_bounds__(128, (D <= 64 ? 4 : (D <= 128 ? 3 : 2)))
 attn_local_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ k_cache,
                      const __nv_bfloat16* __restrict__ v_cache, const int* __restrict__ block_tables, int max_blocks,
@@ -293,7 +314,8 @@ attn_local_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* _
                      __nv_bfloat16* __restrict__ out, long long ldo, int H, int G, int bs, float scale, float softcap,
                      int chunk, int sink, float out_scale, int d_real, int vd_real, long long k_row, long long v_row,
                      int window, const float* __restrict__ slopes, const float* __restrict__ sinks,
-                     const int* __restrict__ tok_seq, const int* __restrict__ positions, float* __restrict__ ws) {
+                     const int* __restrict__ tok_seq, const int* __restrict__ positions, float* __restrict__ ws,
+                     int keep_first, const float* __restrict__ bias, int gate_elem) {
     constexpr int LQ = D + 8, LV = VD + 8;     // padded rows: ldmatrix without bank conflicts, 16-byte aligned
     extern __shared__ __align__(16) unsigned char smem_raw[];
     static_assert(kTcRows == kTcKeys, "the query tile is staged in a key stage");
@@ -360,7 +382,7 @@ attn_local_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* _
     const bool has_sink = sink || sinks;
     float m[2], l[2];
     // the sink: a key without a value whose score is 0 or a learned number per head (kept in the base-2 domain like the rest)
-    float slope2[2];
+    float slope2[2], bias2[2];
     int pr[2], plo[2];
 #pragma unroll
     for (int rr = 0; rr < 2; ++rr) {
@@ -370,6 +392,7 @@ attn_local_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* _
         m[rr] = sink_here ? (sinks ? sinks[hr] * kLog2e : 0.f) : -INFINITY;
         l[rr] = sink_here ? 1.f : 0.f;
         slope2[rr] = slopes ? slopes[hr] * kLog2e : 0.f;
+        bias2[rr] = bias ? bias[hr] * kLog2e : 0.f;
         pr[rr] = DEC ? p0 : p0 + r;
         plo[rr] = lower_edge(pr[rr]);
     }
@@ -387,35 +410,41 @@ attn_local_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* _
         const int blk = bs_shift >= 0 ? kq >> bs_shift : kq / bs;
         return (static_cast<long long>(bt[blk]) * G + g) * bs + (kq - blk * bs);
     };
-    auto load_tile = [&](int k0, int stage) {
+    // keys of a tile are valid up to kmax: the last row's position, or the end of the kept first keys
+    auto load_tile = [&](int k0, int stage, int kmax) {
         __nv_bfloat16* dk = sKs + stage * kTcKeys * LQ;
         __nv_bfloat16* dv = sVs + stage * kTcKeys * LV;
         // rows past the portion and columns past the head's own size become zeros (0 x garbage would not be 0)
         for (int c = threadIdx.x; c < kTcKeys * (D / 8); c += 128) {
             const int r = c / (D / 8), part = c - r * (D / 8);
             const int kp = k0 + r;
-            const bool ok = kp <= p1 && part < dq8;
-            cp_async16_zfill(dk + r * LQ + part * 8, k_cache + slot_of(min(kp, p1)) * k_row + (ok ? part * 8 : 0), ok);
+            const bool ok = kp <= kmax && part < dq8;
+            cp_async16_zfill(dk + r * LQ + part * 8, k_cache + slot_of(min(kp, kmax)) * k_row + (ok ? part * 8 : 0), ok);
         }
         for (int c = threadIdx.x; c < kTcKeys * (VD / 8); c += 128) {
             const int r = c / (VD / 8), part = c - r * (VD / 8);
             const int kp = k0 + r;
-            const bool ok = kp <= p1 && part < dv8;
-            cp_async16_zfill(dv + r * LV + part * 8, v_cache + slot_of(min(kp, p1)) * v_row + (ok ? part * 8 : 0), ok);
+            const bool ok = kp <= kmax && part < dv8;
+            cp_async16_zfill(dv + r * LV + part * 8, v_cache + slot_of(min(kp, kmax)) * v_row + (ok ? part * 8 : 0), ok);
         }
         asm volatile("cp.async.commit_group;" ::: "memory");
     };
-    int n_tiles = (p1 - lo) / kTcKeys + 1, it_first = 0;
+    const int kept_end = min(keep_first, lo);                       // kept keys below every row's window
+    const int n_kept = (kept_end + kTcKeys - 1) / kTcKeys;
+    int n_tiles = n_kept + (p1 - lo) / kTcKeys + 1, it_first = 0;
+    auto tile_k0 = [&](int it) { return it < n_kept ? it * kTcKeys : lo + (it - n_kept) * kTcKeys; };
+    auto tile_kmax = [&](int it) { return it < n_kept ? kept_end - 1 : p1; };
     if constexpr (DEC) {   // this slice's share of the tiles
         const int per = (n_tiles + static_cast<int>(gridDim.z) - 1) / static_cast<int>(gridDim.z);
         it_first = min(n_tiles, static_cast<int>(blockIdx.z) * per);
         n_tiles = min(n_tiles, it_first + per);
     }
-    if (it_first < n_tiles) load_tile(lo + it_first * kTcKeys, it_first & 1);
+    if (it_first < n_tiles) load_tile(tile_k0(it_first), it_first & 1, tile_kmax(it_first));
     for (int it = it_first; it < n_tiles; ++it) {
-        const int k0 = lo + it * kTcKeys;
+        const int k0 = tile_k0(it);
+        const bool kept_tile = it < n_kept;
         if (it + 1 < n_tiles) {
-            load_tile(k0 + kTcKeys, (it + 1) & 1);
+            load_tile(tile_k0(it + 1), (it + 1) & 1, tile_kmax(it + 1));
             asm volatile("cp.async.wait_group 1;" ::: "memory");
         } else {
             asm volatile("cp.async.wait_group 0;" ::: "memory");
@@ -440,7 +469,7 @@ attn_local_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* _
         }
         float mx[2] = {-INFINITY, -INFINITY};
         // only tiles that reach past the warp's first row or start before its last row's block need the mask
-        const bool edge = k0 + kTcKeys - 1 > first_row_pos || k0 < plo_last;
+        const bool edge = kept_tile || k0 + kTcKeys - 1 > first_row_pos || k0 < plo_last;
         if (softcap > 0.f) {
 #pragma unroll
             for (int nb = 0; nb < kTcKeys / 8; ++nb) {
@@ -465,16 +494,32 @@ attn_local_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* _
                 }
             }
         }
+        if (bias) {
+#pragma unroll
+            for (int nb = 0; nb < kTcKeys / 8; ++nb) {
+#pragma unroll
+                for (int e = 0; e < 4; ++e) sc[nb][e] += bias2[e >> 1];
+            }
+        }
         if (edge) {
+            const int kend = kept_tile ? kept_end : 0x7fffffff;   // a kept tile ends where the kept keys (or the window's tiles) end
 #pragma unroll
             for (int nb = 0; nb < kTcKeys / 8; ++nb) {
 #pragma unroll
                 for (int e = 0; e < 4; ++e) {
                     const int col = k0 + nb * 8 + (lane & 3) * 2 + (e & 1);
-                    if (col > pr[e >> 1] || col < plo[e >> 1]) sc[nb][e] = -INFINITY;
+                    if (col > pr[e >> 1] || col >= kend || (col < plo[e >> 1] && col >= keep_first)) sc[nb][e] = -INFINITY;
                 }
             }
         }
+        if constexpr (SIG) {
+            // sigmoid(x) = 1 / (1 + 2^(-x log2 e)); a masked score (-inf) gives 2^inf = inf and 1 / inf = 0
+#pragma unroll
+            for (int nb = 0; nb < kTcKeys / 8; ++nb) {
+#pragma unroll
+                for (int e = 0; e < 4; ++e) sc[nb][e] = rcp_approx(1.f + ex2_approx(-sc[nb][e]));
+            }
+        } else {
 #pragma unroll
         for (int nb = 0; nb < kTcKeys / 8; ++nb) {
 #pragma unroll
@@ -514,6 +559,7 @@ attn_local_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* _
             o[i][2] *= corr[1];
             o[i][3] *= corr[1];
         }
+        }   // softmax
 #pragma unroll
         for (int kk = 0; kk < kTcKeys / 16; ++kk) {
             uint32_t a[4];
@@ -546,20 +592,23 @@ attn_local_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* _
                 if ((lane & 3) == 0) *reinterpret_cast<float2*>(w + VD) = make_float2(m[rr], l[rr]);
                 continue;
             }
-            float mul = out_scale / l[rr];
-            if (gate) mul *= 1.f / (1.f + __expf(-gate[row0 * ldg + h + r]));
-            __nv_bfloat16* orow = out + row0 * ldo + static_cast<long long>(h + r) * vd_real + (lane & 3) * 2;
-#pragma unroll
-            for (int nb = 0; nb < VD / 8; ++nb)
-                if (nb < dv8) *reinterpret_cast<uint32_t*>(orow + nb * 8) = pack_bf16(o[nb][2 * rr] * mul, o[nb][2 * rr + 1] * mul);
-            continue;
         }
-        float mul = out_scale / l[rr];
-        if (gate) mul *= 1.f / (1.f + __expf(-gate[(row0 + r) * ldg + h]));
-        __nv_bfloat16* orow = out + (row0 + r) * ldo + static_cast<long long>(h) * vd_real + (lane & 3) * 2;
+        const long long orow_i = DEC ? row0 : row0 + r;
+        const int oh = DEC ? h + r : h;
+        float mul = SIG ? out_scale : out_scale / l[rr];
+        if (gate && !gate_elem) mul *= 1.f / (1.f + __expf(-gate[orow_i * ldg + oh]));
+        __nv_bfloat16* orow = out + orow_i * ldo + static_cast<long long>(oh) * vd_real + (lane & 3) * 2;
+        const float* grow = (gate && gate_elem) ? gate + orow_i * ldg + static_cast<long long>(oh) * vd_real + (lane & 3) * 2 : nullptr;
 #pragma unroll
-        for (int nb = 0; nb < VD / 8; ++nb)
-            if (nb < dv8) *reinterpret_cast<uint32_t*>(orow + nb * 8) = pack_bf16(o[nb][2 * rr] * mul, o[nb][2 * rr + 1] * mul);
+        for (int nb = 0; nb < VD / 8; ++nb) {
+            if (nb >= dv8) continue;
+            float a = o[nb][2 * rr] * mul, b = o[nb][2 * rr + 1] * mul;
+            if (gate && gate_elem) {
+                a *= 1.f / (1.f + __expf(-grow[nb * 8]));
+                b *= 1.f / (1.f + __expf(-grow[nb * 8 + 1]));
+            }
+            *reinterpret_cast<uint32_t*>(orow + nb * 8) = pack_bf16(a, b);
+        }
     }
 }
 
@@ -568,10 +617,11 @@ static int tc_key_width(int D) { return D <= 64 ? 64 : (D <= 128 ? 128 : (D <= 1
 static int tc_value_width(int Vd) { return Vd <= 64 ? 64 : (Vd <= 128 ? 128 : 0); }
 
 // Folds the slices of the decode form: out = sum_s o_s 2^(m_s - M) / sum_s l_s 2^(m_s - M), M = max_s m_s (base-2 domain).
+// sigmoid_w: the slices hold plain sums of weighted values and are added as they are.
 __global__ void __launch_bounds__(128)
 attn_split_merge_kernel(const float* __restrict__ ws, int splits, int vd_pad, int vd_real, const int* __restrict__ tok_seq,
                         const float* __restrict__ gate, long long ldg, __nv_bfloat16* __restrict__ out, long long ldo, int H,
-                        float out_scale) {
+                        float out_scale, int sigmoid_w, int gate_elem) {
     __shared__ float wgt[64];   // weight of every slice: 2^(m_s - M) / sum (at most 64 slices)
     pdl_launch_dependents();
     pdl_wait();
@@ -581,14 +631,17 @@ attn_split_merge_kernel(const float* __restrict__ ws, int splits, int vd_pad, in
     const float* w = ws + (t * H + h) * splits * (vd_pad + 2);
     if (threadIdx.x < 32) {   // one warp: every lane fetches the maximum and sum of up to two slices at once
         const int lane = threadIdx.x;
-        float m0 = -INFINITY, l0 = 0.f, m1 = -INFINITY, l1 = 0.f;
-        if (lane < splits) m0 = w[lane * (vd_pad + 2) + vd_pad], l0 = w[lane * (vd_pad + 2) + vd_pad + 1];
-        if (lane + 32 < splits) m1 = w[(lane + 32) * (vd_pad + 2) + vd_pad], l1 = w[(lane + 32) * (vd_pad + 2) + vd_pad + 1];
-        const float M = warp_max(fmaxf(m0, m1));
-        const float e0 = m0 == -INFINITY ? 0.f : ex2_approx(m0 - M), e1 = m1 == -INFINITY ? 0.f : ex2_approx(m1 - M);
-        const float den = warp_sum(l0 * e0 + l1 * e1);
-        float mul = out_scale / den;
-        if (gate) mul *= 1.f / (1.f + __expf(-gate[t * ldg + h]));
+        float mul = out_scale, e0 = 1.f, e1 = 1.f;
+        if (!sigmoid_w) {
+            float m0 = -INFINITY, l0 = 0.f, m1 = -INFINITY, l1 = 0.f;
+            if (lane < splits) m0 = w[lane * (vd_pad + 2) + vd_pad], l0 = w[lane * (vd_pad + 2) + vd_pad + 1];
+            if (lane + 32 < splits) m1 = w[(lane + 32) * (vd_pad + 2) + vd_pad], l1 = w[(lane + 32) * (vd_pad + 2) + vd_pad + 1];
+            const float M = warp_max(fmaxf(m0, m1));
+            e0 = m0 == -INFINITY ? 0.f : ex2_approx(m0 - M), e1 = m1 == -INFINITY ? 0.f : ex2_approx(m1 - M);
+            const float den = warp_sum(l0 * e0 + l1 * e1);
+            mul = out_scale / den;
+        }
+        if (gate && !gate_elem) mul *= 1.f / (1.f + __expf(-gate[t * ldg + h]));
         wgt[lane] = e0 * mul;
         wgt[lane + 32] = e1 * mul;
     }
@@ -597,6 +650,7 @@ attn_split_merge_kernel(const float* __restrict__ ws, int splits, int vd_pad, in
         float acc = 0.f;
 #pragma unroll 4
         for (int s = 0; s < splits; ++s) acc = fmaf(w[s * (vd_pad + 2) + d], wgt[s], acc);
+        if (gate && gate_elem) acc *= 1.f / (1.f + __expf(-gate[t * ldg + static_cast<long long>(h) * vd_real + d]));
         out[t * ldo + static_cast<long long>(h) * vd_real + d] = __float2bfloat16_rn(acc);
     }
 }
@@ -604,10 +658,10 @@ attn_split_merge_kernel(const float* __restrict__ ws, int splits, int vd_pad, in
 struct AttnTcArgs {
     const void *q, *k_cache, *v_cache;
     const int *block_tables, *seq_start, *seq_count, *seq_pos0;
-    const float *gate, *slopes, *sinks;
+    const float *gate, *slopes, *sinks, *bias;
     void* out;
     long long ldg, ldo, k_row, v_row;
-    int max_blocks, n_seqs, max_tiles, H, G, D, Vd, bs, chunk, window, sink, flags;
+    int max_blocks, n_seqs, max_tiles, H, G, D, Vd, bs, chunk, window, keep_first, sink, sigmoid_w, gate_elem, flags;
     float scale, softcap, out_scale;
     // decode form: rows listed by tok_seq / positions, slices of the keys, scratch for their partial results
     const int *tok_seq, *positions;
@@ -615,12 +669,12 @@ struct AttnTcArgs {
     int splits;
 };
 
-template <int D, int VD, bool DEC>
+template <int D, int VD, bool DEC, bool SIG>
 static int launch_attn_tc(const AttnTcArgs& a, cudaStream_t stream) {
     const int smem = 2 * kTcKeys * (D + 8) * 2 + 2 * kTcKeys * (VD + 8) * 2;
     static bool attr_done = false;
     if (!attr_done && smem > 48 * 1024) {
-        ATX_CUDA(cudaFuncSetAttribute(attn_local_tc_kernel<D, VD, DEC>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+        ATX_CUDA(cudaFuncSetAttribute(attn_local_tc_kernel<D, VD, DEC, SIG>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
         attr_done = true;
     }
     cudaLaunchConfig_t cfg = {};
@@ -636,34 +690,46 @@ static int launch_attn_tc(const AttnTcArgs& a, cudaStream_t stream) {
         cfg.numAttrs = 1;
     }
     using B = __nv_bfloat16;
-    ATX_CUDA(cudaLaunchKernelEx(&cfg, attn_local_tc_kernel<D, VD, DEC>, reinterpret_cast<const B*>(a.q),
+    ATX_CUDA(cudaLaunchKernelEx(&cfg, attn_local_tc_kernel<D, VD, DEC, SIG>, reinterpret_cast<const B*>(a.q),
                                 reinterpret_cast<const B*>(a.k_cache), reinterpret_cast<const B*>(a.v_cache),
                                 a.block_tables, a.max_blocks, a.seq_start, a.seq_count, a.seq_pos0, a.n_seqs, a.gate, a.ldg,
                                 reinterpret_cast<B*>(a.out), a.ldo, a.H, a.G, a.bs, a.scale, a.softcap, a.chunk, a.sink,
                                 a.out_scale, a.D, a.Vd, a.k_row, a.v_row, a.window, a.slopes, a.sinks, a.tok_seq, a.positions,
-                                a.ws));
+                                a.ws, a.keep_first, a.bias, a.gate_elem));
     if (DEC && a.splits > 1) {
         cfg.gridDim = dim3(a.n_seqs, a.H);
         cfg.dynamicSmemBytes = 0;
         ATX_CUDA(cudaLaunchKernelEx(&cfg, attn_split_merge_kernel, const_cast<const float*>(a.ws), a.splits, VD, a.Vd,
-                                    a.tok_seq, a.gate, a.ldg, reinterpret_cast<B*>(a.out), a.ldo, a.H, a.out_scale));
+                                    a.tok_seq, a.gate, a.ldg, reinterpret_cast<B*>(a.out), a.ldo, a.H, a.out_scale,
+                                    a.sigmoid_w, a.gate_elem));
     }
     return ATX_OK;
 }
 
-template <bool DEC>
-static int dispatch_attn_tc(const AttnTcArgs& a, cudaStream_t st) {
+template <bool DEC, bool SIG>
+static int dispatch_attn_tc_w(const AttnTcArgs& a, cudaStream_t st) {
     const int kw = tc_key_width(a.D), vw = tc_value_width(a.Vd);
     if (vw == 64) {
-        if (kw == 64) return launch_attn_tc<64, 64, DEC>(a, st);
-        if (kw == 128) return launch_attn_tc<128, 64, DEC>(a, st);
-        if (kw == 192) return launch_attn_tc<192, 64, DEC>(a, st);
-        return launch_attn_tc<256, 64, DEC>(a, st);
+        if (kw == 64) return launch_attn_tc<64, 64, DEC, SIG>(a, st);
+        if (kw == 128) return launch_attn_tc<128, 64, DEC, SIG>(a, st);
+        if (kw == 192) return launch_attn_tc<192, 64, DEC, SIG>(a, st);
+        return launch_attn_tc<256, 64, DEC, SIG>(a, st);
     }
-    if (kw == 64) return launch_attn_tc<64, 128, DEC>(a, st);
-    if (kw == 128) return launch_attn_tc<128, 128, DEC>(a, st);
-    if (kw == 192) return launch_attn_tc<192, 128, DEC>(a, st);
-    return launch_attn_tc<256, 128, DEC>(a, st);
+    if (kw == 64) return launch_attn_tc<64, 128, DEC, SIG>(a, st);
+    if (kw == 128) return launch_attn_tc<128, 128, DEC, SIG>(a, st);
+    if (kw == 192) return launch_attn_tc<192, 128, DEC, SIG>(a, st);
+    return launch_attn_tc<256, 128, DEC, SIG>(a, st);
+}
+
+template <bool DEC>
+static int dispatch_attn_tc(const AttnTcArgs& a, cudaStream_t st) {
+    return a.sigmoid_w ? dispatch_attn_tc_w<DEC, true>(a, st) : dispatch_attn_tc_w<DEC, false>(a, st);
+}
+
+static bool opts_ok(const atx_attn_opts* o) {
+    return o && o->chunk >= 0 && o->window >= 0 && o->keep_first >= 0 &&
+           (o->weight == ATX_ATTN_SOFTMAX || o->weight == ATX_ATTN_SIGMOID) &&
+           !(o->weight == ATX_ATTN_SIGMOID && (o->sink || o->sinks));
 }
 
 }  // namespace atx
@@ -720,6 +786,15 @@ int atx_qk_prepare(const float* proj, long long ld, int q_off, int k_off, int v_
     return ATX_OK;
 }
 
+static atx_attn_opts softmax_opts(float scale, float softcap, int chunk, int window, const float* slopes, const float* sinks,
+                                  int sink, float out_scale) {
+    atx_attn_opts o = {};
+    o.scale = scale, o.softcap = softcap, o.out_scale = out_scale;
+    o.chunk = chunk, o.window = window, o.sink = sink, o.weight = ATX_ATTN_SOFTMAX;
+    o.slopes = slopes, o.sinks = sinks;
+    return o;
+}
+
 int atx_attn_local(const void* q, const void* k_cache, const void* v_cache, const int* block_tables, int max_blocks,
                    const int* tok_seq, const int* positions, const float* gate, long long ldg, void* out, long long ldo,
                    int T, int H, int G, int D, int Vd, int block_size, float scale, float softcap, int chunk, int sink,
@@ -734,10 +809,20 @@ int atx_attn_window(const void* q, const void* k_cache, const void* v_cache, lon
                     long long ldg, void* out, long long ldo, int T, int H, int G, int D, int Vd, int block_size,
                     float scale, float softcap, int chunk, int window, const float* slopes, const float* sinks, int sink,
                     float out_scale, int dtype, int flags, atx_stream_t stream) {
-    ATX_REQUIRE(q && k_cache && v_cache && block_tables && tok_seq && positions && out, "atx_attn_window: null pointer");
+    const atx_attn_opts o = softmax_opts(scale, softcap, chunk, window, slopes, sinks, sink, out_scale);
+    return atx_attn_paged(q, k_cache, v_cache, k_row, v_row, block_tables, max_blocks, tok_seq, positions, gate, ldg, out,
+                          ldo, T, H, G, D, Vd, block_size, &o, dtype, flags, stream);
+}
+
+int atx_attn_paged(const void* q, const void* k_cache, const void* v_cache, long long k_row, long long v_row,
+                   const int* block_tables, int max_blocks, const int* tok_seq, const int* positions, const float* gate,
+                   long long ldg, void* out, long long ldo, int T, int H, int G, int D, int Vd, int block_size,
+                   const atx_attn_opts* o, int dtype, int flags, atx_stream_t stream) {
+    ATX_REQUIRE(q && k_cache && v_cache && block_tables && tok_seq && positions && out, "atx_attn_paged: null pointer");
+    ATX_REQUIRE(opts_ok(o), "atx_attn_paged: bad options (negative sizes, unknown weight kind, or a sink with sigmoid weights)");
     ATX_REQUIRE(T > 0 && H > 0 && G > 0 && H % G == 0 && D > 0 && Vd > 0 && Vd <= 32 * kMaxVdPerLane && block_size > 0 &&
-                    chunk >= 0 && window >= 0 && k_row >= D && v_row >= Vd,
-                "atx_attn_window: bad shape T=%d H=%d G=%d D=%d Vd=%d (Vd <= %d) k_row=%lld v_row=%lld", T, H, G, D, Vd,
+                    k_row >= D && v_row >= Vd,
+                "atx_attn_paged: bad shape T=%d H=%d G=%d D=%d Vd=%d (Vd <= %d) k_row=%lld v_row=%lld", T, H, G, D, Vd,
                 32 * kMaxVdPerLane, k_row, v_row);
     cudaLaunchConfig_t cfg = {};
     cudaLaunchAttribute attr[1];
@@ -751,12 +836,14 @@ int atx_attn_window(const void* q, const void* k_cache, const void* v_cache, lon
         cfg.attrs = attr;
         cfg.numAttrs = 1;
     }
+    const int sig = o->weight == ATX_ATTN_SIGMOID ? 1 : 0;
 #define ATX_ATTN_ROW_LAUNCH(XT_, NV_)                                                                                  \
     ATX_CUDA(cudaLaunchKernelEx(&cfg, attn_local_kernel<XT_, NV_>, reinterpret_cast<const XT_*>(q),                    \
                                 reinterpret_cast<const XT_*>(k_cache), reinterpret_cast<const XT_*>(v_cache),          \
                                 block_tables, max_blocks, tok_seq, positions, gate, ldg, reinterpret_cast<XT_*>(out),  \
-                                ldo, H, G, D, Vd, block_size, scale, softcap, chunk, sink, out_scale, k_row, v_row,    \
-                                window, slopes, sinks))
+                                ldo, H, G, D, Vd, block_size, o->scale, o->softcap, o->chunk, o->sink, o->out_scale,   \
+                                k_row, v_row, o->window, o->slopes, o->sinks, o->keep_first, sig, o->bias,             \
+                                o->gate_elem))
 #define ATX_ATTN_ROW_BY_VD(XT_)                        \
     do {                                               \
         if (Vd <= 64) ATX_ATTN_ROW_LAUNCH(XT_, 2);     \
@@ -806,16 +893,34 @@ int atx_attn_window_prefill(const void* q, const void* k_cache, const void* v_ca
                             long long ldo, int H, int G, int D, int Vd, int block_size, float scale, float softcap,
                             int chunk, int window, const float* slopes, const float* sinks, int sink, float out_scale,
                             int dtype, int flags, atx_stream_t stream) {
+    const atx_attn_opts o = softmax_opts(scale, softcap, chunk, window, slopes, sinks, sink, out_scale);
+    return atx_attn_paged_prefill(q, k_cache, v_cache, k_row, v_row, block_tables, max_blocks, seq_start, seq_count, seq_pos0,
+                                  n_seqs, total_rows, gate, ldg, out, ldo, H, G, D, Vd, block_size, &o, dtype, flags, stream);
+}
+
+static void fill_tc_args(AttnTcArgs& a, const atx_attn_opts* o) {
+    a.slopes = o->slopes, a.sinks = o->sinks, a.bias = o->bias;
+    a.chunk = o->chunk, a.window = o->window, a.keep_first = o->keep_first, a.sink = o->sink;
+    a.sigmoid_w = o->weight == ATX_ATTN_SIGMOID ? 1 : 0, a.gate_elem = o->gate_elem;
+    a.scale = o->scale, a.softcap = o->softcap, a.out_scale = o->out_scale;
+}
+
+int atx_attn_paged_prefill(const void* q, const void* k_cache, const void* v_cache, long long k_row, long long v_row,
+                           const int* block_tables, int max_blocks, const int* seq_start, const int* seq_count,
+                           const int* seq_pos0, int n_seqs, int total_rows, const float* gate, long long ldg, void* out,
+                           long long ldo, int H, int G, int D, int Vd, int block_size, const atx_attn_opts* o, int dtype,
+                           int flags, atx_stream_t stream) {
     ATX_REQUIRE(q && k_cache && v_cache && block_tables && seq_start && seq_count && seq_pos0 && out,
-                "atx_attn_window_prefill: null pointer");
-    ATX_REQUIRE(n_seqs > 0 && total_rows > 0 && H > 0 && G > 0 && H % G == 0 && block_size > 0 && chunk >= 0 && window >= 0 &&
-                    k_row >= D && v_row >= Vd && ldo % 2 == 0,
-                "atx_attn_window_prefill: bad shape n_seqs=%d rows=%d H=%d G=%d k_row=%lld v_row=%lld ldo=%lld", n_seqs,
+                "atx_attn_paged_prefill: null pointer");
+    ATX_REQUIRE(opts_ok(o), "atx_attn_paged_prefill: bad options");
+    ATX_REQUIRE(n_seqs > 0 && total_rows > 0 && H > 0 && G > 0 && H % G == 0 && block_size > 0 && k_row >= D && v_row >= Vd &&
+                    ldo % 2 == 0 && (!o->gate_elem || ldg % 2 == 0),
+                "atx_attn_paged_prefill: bad shape n_seqs=%d rows=%d H=%d G=%d k_row=%lld v_row=%lld ldo=%lld", n_seqs,
                 total_rows, H, G, k_row, v_row, ldo);
     if (!atx_attn_window_prefill_supported(D, Vd, k_row, v_row, dtype) ||
         ((reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(k_cache) | reinterpret_cast<uintptr_t>(v_cache)) & 15) ||
         (reinterpret_cast<uintptr_t>(out) & 3)) {
-        set_error("atx_attn_window_prefill: bf16, 16-byte aligned buffers, head and row sizes in multiples of 8, key size "
+        set_error("atx_attn_paged_prefill: bf16, 16-byte aligned buffers, head and row sizes in multiples of 8, key size "
                   "<= 256 and value size <= 128 only; got D=%d Vd=%d k_row=%lld v_row=%lld dtype=%d", D, Vd, k_row, v_row,
                   dtype);
         return ATX_ERR_UNSUPPORTED;
@@ -823,12 +928,12 @@ int atx_attn_window_prefill(const void* q, const void* k_cache, const void* v_ca
     AttnTcArgs a = {};
     a.q = q, a.k_cache = k_cache, a.v_cache = v_cache;
     a.block_tables = block_tables, a.seq_start = seq_start, a.seq_count = seq_count, a.seq_pos0 = seq_pos0;
-    a.gate = gate, a.slopes = slopes, a.sinks = sinks, a.out = out;
+    a.gate = gate, a.out = out;
     a.ldg = ldg, a.ldo = ldo, a.k_row = k_row, a.v_row = v_row;
     a.max_blocks = max_blocks, a.n_seqs = n_seqs;
     a.max_tiles = (total_rows + kTcRows - 1) / kTcRows + n_seqs;   // every sequence adds at most one partly filled tile
-    a.H = H, a.G = G, a.D = D, a.Vd = Vd, a.bs = block_size, a.chunk = chunk, a.window = window, a.sink = sink, a.flags = flags;
-    a.scale = scale, a.softcap = softcap, a.out_scale = out_scale;
+    a.H = H, a.G = G, a.D = D, a.Vd = Vd, a.bs = block_size, a.flags = flags;
+    fill_tc_args(a, o);
     return dispatch_attn_tc<false>(a, reinterpret_cast<cudaStream_t>(stream));
 }
 
@@ -848,31 +953,43 @@ int atx_attn_window_decode(const void* q, const void* k_cache, const void* v_cac
                            long long workspace_bytes, int splits, int T, int H, int G, int D, int Vd, int block_size,
                            float scale, float softcap, int chunk, int window, const float* slopes, const float* sinks,
                            int sink, float out_scale, int dtype, int flags, atx_stream_t stream) {
-    ATX_REQUIRE(q && k_cache && v_cache && block_tables && tok_seq && positions && out, "atx_attn_window_decode: null pointer");
-    ATX_REQUIRE(T > 0 && H > 0 && G > 0 && H % G == 0 && block_size > 0 && chunk >= 0 && window >= 0 && k_row >= D &&
-                    v_row >= Vd && ldo % 2 == 0 && splits >= 1 && splits <= 64 && G <= 65535,
-                "atx_attn_window_decode: bad shape T=%d H=%d G=%d k_row=%lld v_row=%lld ldo=%lld splits=%d", T, H, G, k_row,
+    const atx_attn_opts o = softmax_opts(scale, softcap, chunk, window, slopes, sinks, sink, out_scale);
+    return atx_attn_paged_decode(q, k_cache, v_cache, k_row, v_row, block_tables, max_blocks, tok_seq, positions, gate, ldg,
+                                 out, ldo, workspace, workspace_bytes, splits, T, H, G, D, Vd, block_size, &o, dtype, flags,
+                                 stream);
+}
+
+int atx_attn_paged_decode(const void* q, const void* k_cache, const void* v_cache, long long k_row, long long v_row,
+                          const int* block_tables, int max_blocks, const int* tok_seq, const int* positions,
+                          const float* gate, long long ldg, void* out, long long ldo, void* workspace,
+                          long long workspace_bytes, int splits, int T, int H, int G, int D, int Vd, int block_size,
+                          const atx_attn_opts* o, int dtype, int flags, atx_stream_t stream) {
+    ATX_REQUIRE(q && k_cache && v_cache && block_tables && tok_seq && positions && out, "atx_attn_paged_decode: null pointer");
+    ATX_REQUIRE(opts_ok(o), "atx_attn_paged_decode: bad options");
+    ATX_REQUIRE(T > 0 && H > 0 && G > 0 && H % G == 0 && block_size > 0 && k_row >= D && v_row >= Vd && ldo % 2 == 0 &&
+                    splits >= 1 && splits <= 64 && G <= 65535 && (!o->gate_elem || ldg % 2 == 0),
+                "atx_attn_paged_decode: bad shape T=%d H=%d G=%d k_row=%lld v_row=%lld ldo=%lld splits=%d", T, H, G, k_row,
                 v_row, ldo, splits);
     if (!atx_attn_window_decode_supported(H, G, D, Vd, k_row, v_row, dtype) ||
         ((reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(k_cache) | reinterpret_cast<uintptr_t>(v_cache)) & 15) ||
         (reinterpret_cast<uintptr_t>(out) & 3)) {
-        set_error("atx_attn_window_decode: bf16, 16-byte aligned buffers, sizes in multiples of 8, key size <= 256, value "
+        set_error("atx_attn_paged_decode: bf16, 16-byte aligned buffers, sizes in multiples of 8, key size <= 256, value "
                   "size <= 128, at most 64 query heads per key/value head; got H=%d G=%d D=%d Vd=%d dtype=%d", H, G, D, Vd,
                   dtype);
         return ATX_ERR_UNSUPPORTED;
     }
     ATX_REQUIRE(workspace_bytes >= atx_attn_window_decode_workspace_bytes(T, H, Vd, splits) &&
                     (splits == 1 || (workspace && (reinterpret_cast<uintptr_t>(workspace) & 7) == 0)),
-                "atx_attn_window_decode: %d slices need %lld bytes of scratch (8-byte aligned), got %lld", splits,
+                "atx_attn_paged_decode: %d slices need %lld bytes of scratch (8-byte aligned), got %lld", splits,
                 atx_attn_window_decode_workspace_bytes(T, H, Vd, splits), workspace_bytes);
     AttnTcArgs a = {};
     a.q = q, a.k_cache = k_cache, a.v_cache = v_cache;
     a.block_tables = block_tables, a.tok_seq = tok_seq, a.positions = positions;
-    a.gate = gate, a.slopes = slopes, a.sinks = sinks, a.out = out;
+    a.gate = gate, a.out = out;
     a.ldg = ldg, a.ldo = ldo, a.k_row = k_row, a.v_row = v_row;
     a.max_blocks = max_blocks, a.n_seqs = T, a.splits = splits, a.ws = reinterpret_cast<float*>(workspace);
-    a.H = H, a.G = G, a.D = D, a.Vd = Vd, a.bs = block_size, a.chunk = chunk, a.window = window, a.sink = sink, a.flags = flags;
-    a.scale = scale, a.softcap = softcap, a.out_scale = out_scale;
+    a.H = H, a.G = G, a.D = D, a.Vd = Vd, a.bs = block_size, a.flags = flags;
+    fill_tc_args(a, o);
     return dispatch_attn_tc<true>(a, reinterpret_cast<cudaStream_t>(stream));
 }
 

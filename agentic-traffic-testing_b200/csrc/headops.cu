@@ -185,7 +185,8 @@ head_prepare_kernel(const float* __restrict__ src, long long ld, const int* __re
         (s.dst_kind == ATX_HEAD_DST_PAGES || (s.dst_ld & 3) == 0) &&
         ((reinterpret_cast<unsigned long long>(src) | reinterpret_cast<unsigned long long>(s.dst) |
           reinterpret_cast<unsigned long long>(s.norm_w) | reinterpret_cast<unsigned long long>(s.mix_src) |
-          reinterpret_cast<unsigned long long>(s.save)) & 15) == 0;
+          reinterpret_cast<unsigned long long>(s.save)) & 15) == 0 &&
+        (!s.rot_half || (half & 3) == 0);   // half-split pairs: the partner's four elements are one more aligned access
     if (vec) {
         if (s.norm_dims > 0) {
             float ss = 0.f;
@@ -206,9 +207,29 @@ head_prepare_kernel(const float* __restrict__ src, long long ld, const int* __re
                 const float4 g = hld4(nw, i4);
                 e[0] *= r * g.x, e[1] *= r * g.y, e[2] *= r * g.z, e[3] *= r * g.w;
             }
+            if (s.rot_half) {
+                // element j < half pairs with j + half: (u, w) -> (u c - w s, w c + u s), angle index j mod half
+                const int j = i - s.rot_off;
+                if (j >= 0 && j < s.rot_dims) {
+                    const bool low = j < half;
+                    const int ip4 = low ? i4 + half / 4 : i4 - half / 4;
+                    const float4 pv = hld4(x, ip4);
+                    float pe[4] = {pv.x, pv.y, pv.z, pv.w};
+                    if (4 * ip4 < s.norm_dims) {
+                        const float4 g = hld4(nw, ip4);
+                        pe[0] *= r * g.x, pe[1] *= r * g.y, pe[2] *= r * g.z, pe[3] *= r * g.w;
+                    }
+                    const int a0 = low ? j : j - half;
+#pragma unroll
+                    for (int q = 0; q < 4; ++q) {
+                        const float c = cs[a0 + q], sn = cs[half + a0 + q];
+                        e[q] = low ? fmaf(e[q], c, -(pe[q] * sn)) : fmaf(e[q], c, pe[q] * sn);
+                    }
+                }
+            }
 #pragma unroll
             for (int p2 = 0; p2 < 2; ++p2) {
-                const int j = i + 2 * p2 - s.rot_off;
+                const int j = s.rot_half ? -1 : i + 2 * p2 - s.rot_off;
                 if (j >= 0 && j < s.rot_dims) {
                     const float c = cs[j >> 1], sn = cs[half + (j >> 1)];
                     const float a0 = e[2 * p2], b0 = e[2 * p2 + 1];
@@ -242,10 +263,18 @@ head_prepare_kernel(const float* __restrict__ src, long long ld, const int* __re
         float v = normed(i);
         const int j = i - s.rot_off;
         if (j >= 0 && j < s.rot_dims) {
-            const float p = normed(s.rot_off + (j ^ 1));
-            const float c = cs[j >> 1], sn = cs[half + (j >> 1)];
-            // pair (u, w) -> (u c - w s, w c + u s)
-            v = (j & 1) ? fmaf(v, c, p * sn) : fmaf(v, c, -(p * sn));
+            if (s.rot_half) {
+                const bool low = j < half;
+                const float p = normed(s.rot_off + (low ? j + half : j - half));
+                const int a0 = low ? j : j - half;
+                const float c = cs[a0], sn = cs[half + a0];
+                v = low ? fmaf(v, c, -(p * sn)) : fmaf(v, c, p * sn);
+            } else {
+                const float p = normed(s.rot_off + (j ^ 1));
+                const float c = cs[j >> 1], sn = cs[half + (j >> 1)];
+                // pair (u, w) -> (u c - w s, w c + u s)
+                v = (j & 1) ? fmaf(v, c, p * sn) : fmaf(v, c, -(p * sn));
+            }
         }
         if (s.save) s.save[flat + i] = v;
         if (s.mix_src) v = fmaf(s.mix, s.mix_src[flat + i] - v, v);   // (1 - mix) v + mix m

@@ -120,12 +120,14 @@ __global__ void __launch_bounds__(128) concat_embed_kernel(const float* __restri
 // With `rows` the residual itself is left untouched (the gathered rows feed the LM head only).
 // zero_y: the row of y is cleared once it has been read, so that the next split-K GEMM can accumulate into it;
 // CTAs beyond T clear zero_ptr (the accumulator of the GEMM that consumes `out`).
-template <typename XT, bool VEC>
+// post_scale (nullable): a second weight vector on the post-normed sublayer output (a learned scale per channel of the
+// residual branch). OT: the element type of `out`, XT or fp32 (a consumer that still works on the normed row in fp32).
+template <typename XT, typename OT, bool VEC>
 __global__ void __launch_bounds__(1024)
 resid_norm_kernel(float* __restrict__ h, float* __restrict__ y, const XT* __restrict__ w_post,
-                  const XT* __restrict__ vec, const XT* __restrict__ w_pre, XT* __restrict__ out,
-                  const int* __restrict__ rows, int T, int W, float eps, int zero_y, uint4* __restrict__ zero_ptr,
-                  long long zero_vecs) {
+                  const XT* __restrict__ post_scale, const XT* __restrict__ vec, const XT* __restrict__ w_pre,
+                  OT* __restrict__ out, const int* __restrict__ rows, int T, int W, float eps, int zero_y,
+                  uint4* __restrict__ zero_ptr, long long zero_vecs) {
     extern __shared__ __align__(16) float srow[];
     __shared__ float red[32];
     pdl_launch_dependents();
@@ -136,6 +138,10 @@ resid_norm_kernel(float* __restrict__ h, float* __restrict__ y, const XT* __rest
     float4 wp4 = make_float4(0.f, 0.f, 0.f, 0.f), vc4 = wp4, wq4 = wp4;
     if (VEC && on) {
         if (w_post) wp4 = ld4(w_post, threadIdx.x);
+        if (post_scale) {
+            const float4 l4 = ld4(post_scale, threadIdx.x);
+            wp4.x *= l4.x, wp4.y *= l4.y, wp4.z *= l4.z, wp4.w *= l4.w;
+        }
         if (vec) vc4 = ld4(vec, threadIdx.x);
         if (w_pre) wq4 = ld4(w_pre, threadIdx.x);
     }
@@ -189,7 +195,12 @@ resid_norm_kernel(float* __restrict__ h, float* __restrict__ y, const XT* __rest
         for (int i = threadIdx.x; i < W4; i += blockDim.x) {
             float4 v = ld4(hr, i);
             if (y) {
-                const float4 a = srow4[i], wp = ld4(w_post, i);
+                const float4 a = srow4[i];
+                float4 wp = ld4(w_post, i);
+                if (post_scale) {
+                    const float4 l4 = ld4(post_scale, i);
+                    wp.x *= l4.x, wp.y *= l4.y, wp.z *= l4.z, wp.w *= l4.w;
+                }
                 v.x += a.x * rs_y * wp.x, v.y += a.y * rs_y * wp.y, v.z += a.z * rs_y * wp.z, v.w += a.w * rs_y * wp.w;
             }
             if (vec) {
@@ -202,7 +213,7 @@ resid_norm_kernel(float* __restrict__ h, float* __restrict__ y, const XT* __rest
         }
         if (!w_pre) return;
         const float rs = rsqrtf(block_sum(ss, red) / static_cast<float>(W) + eps);
-        XT* o = out + static_cast<long long>(t) * W;
+        OT* o = out + static_cast<long long>(t) * W;
         for (int i = threadIdx.x; i < W4; i += blockDim.x) {
             const float4 a = srow4[i], wq = ld4(w_pre, i);
             st4(o, i, make_float4(a.x * rs * wq.x, a.y * rs * wq.y, a.z * rs * wq.z, a.w * rs * wq.w));
@@ -222,7 +233,7 @@ resid_norm_kernel(float* __restrict__ h, float* __restrict__ y, const XT* __rest
     float ss = 0.f;
     for (int i = threadIdx.x; i < W; i += blockDim.x) {
         float v = hr[i];
-        if (y) v += srow[i] * rs_y * ldf(w_post, i);
+        if (y) v += srow[i] * rs_y * (post_scale ? ldf(w_post, i) * ldf(post_scale, i) : ldf(w_post, i));
         if (vec) v += ldf(vec, i);
         if ((y || vec) && !rows) hr[i] = v;
         srow[i] = v;
@@ -230,7 +241,7 @@ resid_norm_kernel(float* __restrict__ h, float* __restrict__ y, const XT* __rest
     }
     if (!w_pre) return;
     const float rs = rsqrtf(block_sum(ss, red) / static_cast<float>(W) + eps);
-    XT* o = out + static_cast<long long>(t) * W;
+    OT* o = out + static_cast<long long>(t) * W;
     for (int i = threadIdx.x; i < W; i += blockDim.x) stf(o, i, srow[i] * rs * ldf(w_pre, i));
 }
 
@@ -672,7 +683,15 @@ int atx_concat_embed(const float* h, const int* ids, const void* table, void* ou
 int atx_resid_norm(float* h, float* y, const void* w_post, const void* vec, const void* w_pre, void* out,
                    const int* rows, int T, int W, float eps, int zero_y, void* zero_ptr, long long zero_bytes, int dtype,
                    int flags, atx_stream_t stream) {
+    return atx_resid_norm_scaled(h, y, w_post, nullptr, vec, w_pre, out, 0, rows, T, W, eps, zero_y, zero_ptr, zero_bytes,
+                                 dtype, flags, stream);
+}
+
+int atx_resid_norm_scaled(float* h, float* y, const void* w_post, const void* post_scale, const void* vec,
+                          const void* w_pre, void* out, int out_f32, const int* rows, int T, int W, float eps, int zero_y,
+                          void* zero_ptr, long long zero_bytes, int dtype, int flags, atx_stream_t stream) {
     ATX_REQUIRE(h, "atx_resid_norm: null pointer");
+    ATX_REQUIRE(!post_scale || w_post, "atx_resid_norm: post_scale needs y and w_post");
     ATX_REQUIRE(T > 0 && W > 0 && W <= 12288, "atx_resid_norm: bad shape T=%d W=%d (W <= 12288)", T, W);
     ATX_REQUIRE((y == nullptr) == (w_post == nullptr), "atx_resid_norm: y and w_post come together");
     ATX_REQUIRE((w_pre == nullptr) == (out == nullptr), "atx_resid_norm: w_pre and out come together");
@@ -690,17 +709,25 @@ int atx_resid_norm(float* h, float* y, const void* w_post, const void* vec, cons
     cfg.stream = reinterpret_cast<cudaStream_t>(stream);
     set_pdl2(cfg, attr, flags);
     auto al16 = [](const void* p) { return reinterpret_cast<uintptr_t>(p) % 16 == 0; };
-    const bool v4 = W % 4 == 0 && al16(h) && al16(y) && al16(w_post) && al16(vec) && al16(w_pre) && al16(out);
-#define ATX_RESID(VEC_)                                                                                                   \
+    const bool v4 = W % 4 == 0 && al16(h) && al16(y) && al16(w_post) && al16(post_scale) && al16(vec) && al16(w_pre) &&
+                    al16(out);
+#define ATX_RESID(OT_, VEC_)                                                                                              \
     ATX_DISPATCH_XT(dtype, ATX_CUDA(cudaLaunchKernelEx(                                                                   \
-                               &cfg, resid_norm_kernel<XT, VEC_>, h, y, reinterpret_cast<const XT*>(w_post),              \
-                               reinterpret_cast<const XT*>(vec), reinterpret_cast<const XT*>(w_pre),                      \
-                               reinterpret_cast<XT*>(out), rows, T, W, eps, zero_y, reinterpret_cast<uint4*>(zero_ptr),   \
-                               zv)))
-    if (v4)
-        ATX_RESID(true);
-    else
-        ATX_RESID(false);
+                               &cfg, resid_norm_kernel<XT, OT_, VEC_>, h, y, reinterpret_cast<const XT*>(w_post),         \
+                               reinterpret_cast<const XT*>(post_scale), reinterpret_cast<const XT*>(vec),                 \
+                               reinterpret_cast<const XT*>(w_pre), reinterpret_cast<OT_*>(out), rows, T, W, eps, zero_y,  \
+                               reinterpret_cast<uint4*>(zero_ptr), zv)))
+    if (out_f32) {
+        if (v4)
+            ATX_RESID(float, true);
+        else
+            ATX_RESID(float, false);
+    } else {
+        if (v4)
+            ATX_RESID(XT, true);
+        else
+            ATX_RESID(XT, false);
+    }
 #undef ATX_RESID
     return ATX_OK;
 }

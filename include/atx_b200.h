@@ -324,7 +324,8 @@ int atx_unary_act(const float* in, long long ldi, void* out, long long ldo, int 
 /* One slice of a fused projection row, cut into `heads` heads of `width` elements (head h starts at column
  * src_off + h * src_stride). Per head, in this order: the first norm_dims elements are divided by their root mean square
  * (eps under the root) and multiplied by norm_w; the elements [rot_off, rot_off + rot_dims) are rotated in adjacent pairs
- * by the angles of rot [max_pos, rot_dims] (cosines, then sines) at the row's position; `save` (fp32 [T, heads * width])
+ * (or, with rot_half, in pairs half the range apart) by the angles of rot [max_pos, rot_dims] (cosines, then sines) at
+ * the row's position; `save` (fp32 [T, heads * width])
  * receives the result; with mix_src (same shape) the result becomes (1 - mix) * result + mix * mix_src. It is written as
  * the element type to rows (dst [T, dst_ld], head h at column dst_off + h * dst_stride) or to pages
  * (dst [blocks, heads, block_size, dst_stride], at the row's slot, from column dst_off of the token's row). */
@@ -336,7 +337,7 @@ typedef struct atx_head_seg {
     int norm_dims, rot_off, rot_dims;
     int dst_kind, dst_off, dst_stride;
     float mix;
-    int reserved;
+    int rot_half; /* 0: adjacent pairs (2i, 2i+1); 1: element i pairs with i + rot_dims/2, angle i of the table */
     const void* norm_w;
     const float* rot;
     const float* mix_src;
@@ -388,6 +389,89 @@ int atx_attn_window_decode(const void* q, const void* k_cache, const void* v_cac
                            long long workspace_bytes, int splits, int T, int H, int G, int D, int Vd, int block_size,
                            float scale, float softcap, int chunk, int window, const float* slopes, const float* sinks,
                            int sink, float out_scale, int dtype, int flags, atx_stream_t stream);
+
+/* ---- Further mechanisms: a residual branch scale, rows that read their predecessor, attention without a softmax,
+ * a polynomial activation of unit-rms powers, a mixture of experts. (Zonidra is built from these; every constant is an
+ * argument.) */
+
+/* atx_resid_norm with a second weight vector on the post-normed sublayer output, h[r] += rms(y[r]) * w_post * post_scale
+ * (post_scale nullable), and with `out` as fp32 when out_f32 != 0 (else the element type). */
+int atx_resid_norm_scaled(float* h, float* y, const void* w_post, const void* post_scale, const void* vec,
+                          const void* w_pre, void* out, int out_f32, const int* rows, int T, int W, float eps, int zero_y,
+                          void* zero_ptr, long long zero_bytes, int dtype, int flags, atx_stream_t stream);
+/* out[t, :] = table[ids[t], :] * scale + pair_table[r, :] with r = (ids[t-1] * mul_prev + ids[t] * mul_cur) mod buckets, or
+ * r = buckets (the table's last row) for the first token of a sequence. The predecessor of a step's first row is
+ * prev_tok[seq_slot[s]], which then receives the step's last token of the sequence. Rows with tok_seq < 0 become zeros. */
+int atx_embed_rows_pair(const int* ids, const void* table, float scale, const void* pair_table, int buckets, int mul_prev,
+                        int mul_cur, int* prev_tok, const int* tok_seq, const int* seq_start, const int* seq_count,
+                        const int* seq_pos0, const int* seq_slot, float* out, int T, int W, int V, int dtype, int flags,
+                        atx_stream_t stream);
+/* out[t, :] = x[t, :] + (x[t-1, :] - x[t, :]) * mu (element type out, x fp32); x[-1] of a sequence is zero, the
+ * predecessor of a step's first row is state[seq_slot[s], :] (fp32 [slots, W]), which then receives the step's last row. */
+int atx_token_shift(const float* x, const void* mu, float* state, const int* tok_seq, const int* seq_start,
+                    const int* seq_count, const int* seq_pos0, const int* seq_slot, void* out, int T, int W, int dtype,
+                    int flags, atx_stream_t stream);
+/* out[t, i] = a z / rms(z) + b z^2 / rms(z^2) + c z^3 / rms(z^3) + e, z = z[t, i], each rms over the row's F elements
+ * (eps under the root); coef = {a, b, c, e} fp32 on the device. */
+int atx_poly_norm_act(const float* z, long long ldz, const float* coef, void* out, long long ldo, int T, int F, float eps,
+                      int dtype, int flags, atx_stream_t stream);
+
+/* Options of the paged attention kernels (atx_attn_window* take the soft-max subset of them as plain arguments).
+ * A query at position p sees key j when j <= p, floor(j / chunk) == floor(p / chunk) (chunk > 0), and j > p - window
+ * (window > 0) or j < keep_first. score = cap(scale q.k) - slopes[h] (p - j) + bias[h]. weight SOFTMAX: soft-max over the
+ * visible keys, `sink` / `sinks` adding exp(0) / exp(sinks[h]) to the denominator; SIGMOID: each visible key weighs
+ * sigmoid(score), nothing is normalised (no sink). gate [T, H], or [T, H * Vd] with gate_elem: out *= sigmoid(gate). */
+#define ATX_ATTN_SOFTMAX 0
+#define ATX_ATTN_SIGMOID 1
+typedef struct atx_attn_opts {
+    float scale, softcap, out_scale;
+    int chunk, window, keep_first, sink;
+    int weight, gate_elem;
+    const float* slopes;
+    const float* sinks;
+    const float* bias;
+} atx_attn_opts;
+/* The three attention entry points with every option: rows one by one (any element type), prompt portions on the tensor
+ * cores, single decoded tokens on the tensor cores (see atx_attn_window, _prefill, _decode for shapes and limits). */
+int atx_attn_paged(const void* q, const void* k_cache, const void* v_cache, long long k_row, long long v_row,
+                   const int* block_tables, int max_blocks, const int* tok_seq, const int* positions, const float* gate,
+                   long long ldg, void* out, long long ldo, int T, int H, int G, int D, int Vd, int block_size,
+                   const atx_attn_opts* opts, int dtype, int flags, atx_stream_t stream);
+int atx_attn_paged_prefill(const void* q, const void* k_cache, const void* v_cache, long long k_row, long long v_row,
+                           const int* block_tables, int max_blocks, const int* seq_start, const int* seq_count,
+                           const int* seq_pos0, int n_seqs, int total_rows, const float* gate, long long ldg, void* out,
+                           long long ldo, int H, int G, int D, int Vd, int block_size, const atx_attn_opts* opts, int dtype,
+                           int flags, atx_stream_t stream);
+int atx_attn_paged_decode(const void* q, const void* k_cache, const void* v_cache, long long k_row, long long v_row,
+                          const int* block_tables, int max_blocks, const int* tok_seq, const int* positions,
+                          const float* gate, long long ldg, void* out, long long ldo, void* workspace,
+                          long long workspace_bytes, int splits, int T, int H, int G, int D, int Vd, int block_size,
+                          const atx_attn_opts* opts, int dtype, int flags, atx_stream_t stream);
+
+/* Mixture of experts. logits [T, ld] fp32 hold R router outputs per token: soft-max over all R; the `top` largest of
+ * score + correction[r] (correction nullable; lowest index on ties) are chosen: sel [T, top] int32, wgt [T, top] = score *
+ * scale. At most 512 outputs. */
+int atx_moe_route(const float* logits, long long ld, const float* correction, int R, int top, float scale, int* sel,
+                  float* wgt, int T, int flags, atx_stream_t stream);
+/* Sorts the n_pairs = T * top (token, choice) pairs by expert. Choices >= E (or < 0) take no slot. seg_off [E + 1]: first
+ * slot of every expert; perm [n_pairs]: pair of a slot; slot_of [n_pairs]: slot of a pair (-1: none); tiles
+ * [2 + 2 * max_tiles] int32: the tile count, a spare word, then (expert, first slot) per tile of atx_moe_tile_rows() slots;
+ * max_tiles = ceil(n_pairs / tile rows) + E always suffices. */
+int atx_moe_tile_rows(void);
+int atx_moe_plan(const int* sel, int n_pairs, int E, int* seg_off, int* perm, int* slot_of, int* tiles, int flags,
+                 atx_stream_t stream);
+/* out[slot, n] = sum_k A[row(slot), k] * W[e * expert_stride + n * ldw + k] for the slots of every expert e; row(slot) =
+ * perm[slot] / top with gather != 0, else slot. gated == 0: fp32 out. gated != 0: W holds N gate rows then N up rows per
+ * expert and out (element type) = silu(gate) * up. bf16 on the tensor cores, fp32 on the FMA pipe. The grid covers
+ * max_tiles tiles; CTAs beyond the plan's count return. */
+int atx_moe_expert_gemm(const void* A, long long lda, const int* perm, int top, int gather, const void* W,
+                        long long expert_stride, long long ldw, void* out, long long ldo, int N, int K, int gated,
+                        const int* seg_off, const int* tiles, int max_tiles, int dtype, int flags, atx_stream_t stream);
+/* y[t, :] = sigmoid(shared_gate[t * ldsg]) * y[t, :] (shared_gate nullable: y is overwritten) + sum_k wgt[t, k] *
+ * (sel[t, k] >= E ? x[t, :] : ye[slot_of[t * top + k], :]). y, ye fp32; x of the element type. */
+int atx_moe_combine(float* y, const float* ye, long long lde, const void* x, const int* sel, const float* wgt,
+                    const int* slot_of, const float* shared_gate, long long ldsg, int T, int W, int top, int E, int dtype,
+                    int flags, atx_stream_t stream);
 
 #ifdef __cplusplus
 }
