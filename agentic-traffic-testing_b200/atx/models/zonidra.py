@@ -242,6 +242,7 @@ class _Layer:
         self.w_egu = self.w_edown = None     # [experts, 2 ff, width] (gate rows, then up rows), [experts, width, ff]
         self.w_sgu = self.w_sdown = None     # shared expert
         self.sgu_interleaved = False
+        self.egu_interleaved = False         # gate / up rows of every expert in blocks of 64, as the gated GEMM epilogue reads them
 
 
 class Weights:
@@ -343,8 +344,16 @@ class Weights:
                     E = int(mlp["router"]["experts"])
                     rows = [get(f + "router")] + ([get(f + "shared.sg")] if mlp.get("shared") else [])
                     l.w_router, l.correction = dev(torch.cat(rows, 0)), f32(get(f + "correction"))
-                    l.w_egu = torch.stack([dev(torch.cat([get(f"{f}e{e}.gate"), get(f"{f}e{e}.up")], 0))
-                                           for e in range(E)], 0).contiguous()
+                    Fe = int(mlp["expert"]["ff"])
+                    if _use_tc(dtype, W) and Fe % 64 == 0:
+                        from ..weights import interleave_gate_up
+
+                        l.egu_interleaved = True
+                        l.w_egu = torch.stack([dev(interleave_gate_up(get(f"{f}e{e}.gate"), get(f"{f}e{e}.up")))
+                                               for e in range(E)], 0).contiguous()
+                    else:
+                        l.w_egu = torch.stack([dev(torch.cat([get(f"{f}e{e}.gate"), get(f"{f}e{e}.up")], 0))
+                                               for e in range(E)], 0).contiguous()
                     l.w_edown = torch.stack([dev(get(f"{f}e{e}.down")) for e in range(E)], 0).contiguous()
                     if mlp.get("shared"):
                         gate, up = get(f + "shared.gate"), get(f + "shared.up")
@@ -631,10 +640,10 @@ class Program:
                                     self.slot_of.data_ptr(), self.tiles.data_ptr(), fl, st))
                 tiles = min(self.max_tiles, (T * top + self.tile_rows - 1) // self.tile_rows + E)
                 ck(lib.atx_moe_expert_gemm(xn, W, self.perm.data_ptr(), top, 1, l.w_egu.data_ptr(), 2 * Fe * W, W,
-                                           self.eact.data_ptr(), Fe, Fe, W, 1, self.seg_off.data_ptr(), self.tiles.data_ptr(),
-                                           tiles, dt, fl, st))
+                                           self.eact.data_ptr(), Fe, Fe, W, 1, 1 if l.egu_interleaved else 0,
+                                           self.seg_off.data_ptr(), self.tiles.data_ptr(), tiles, dt, fl, st))
                 ck(lib.atx_moe_expert_gemm(self.eact.data_ptr(), Fe, None, top, 0, l.w_edown.data_ptr(), W * Fe, Fe,
-                                           self.ye.data_ptr(), W, W, Fe, 0, self.seg_off.data_ptr(), self.tiles.data_ptr(),
+                                           self.ye.data_ptr(), W, W, Fe, 0, 0, self.seg_off.data_ptr(), self.tiles.data_ptr(),
                                            tiles, dt, fl, st))
                 n += 5
                 if shared:

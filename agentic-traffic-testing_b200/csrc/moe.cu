@@ -148,16 +148,28 @@ moe_plan_kernel(const int* __restrict__ sel, int n_pairs, int E, int tile_rows, 
     }
 }
 
-constexpr int kET = 64, kEK = 64, kELD = kEK + 8;
+constexpr int kET = 64, kEK = 64, kELD = kEK + 8, kEStages = 3;
 
-// bf16, tensor cores. A row of slot p: A[(gather ? perm[p] / top : p) * lda]. GATED: two accumulator sets (gate, up).
+__device__ __forceinline__ void moe_cp16(void* smem_dst, const void* gsrc, bool valid) {
+    const uint32_t sz = valid ? 16u : 0u;   // source size 0: sixteen bytes of zeros, nothing is read
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(smem_u32(smem_dst)), "l"(gsrc), "r"(sz) : "memory");
+}
+
+// bf16, tensor cores. A row of slot p: A[(gather ? perm[p] / top : p) * lda]. GATED: two accumulator sets (gate, up);
+// the gate row of output n is row n of the expert's matrix and its up row N + n, or, with `interleaved`, rows
+// 128 (n / 64) + n % 64 and 64 further (the layout of the tcgen05 GEMM's gated epilogue). Tiles of 64 reduction
+// elements arrive by cp.async into three stages, two in flight while one is multiplied: with one or two rows per expert
+// (decoded tokens) the kernel only streams the chosen experts' matrices, and what bounds it is bytes in flight.
 template <bool GATED>
 __global__ void __launch_bounds__(128)
 moe_gemm_tc_kernel(const __nv_bfloat16* __restrict__ A, long long lda, const int* __restrict__ perm, int top, int gather,
                    const __nv_bfloat16* __restrict__ W, long long expert_stride, long long ldw, void* __restrict__ out,
-                   long long ldo, int N, int K, const int* __restrict__ seg_off, const int* __restrict__ tiles) {
-    __shared__ __align__(16) __nv_bfloat16 sa[kET * kELD];
-    __shared__ __align__(16) __nv_bfloat16 sw[(GATED ? 2 : 1) * kET * kELD];
+                   long long ldo, int N, int K, const int* __restrict__ seg_off, const int* __restrict__ tiles,
+                   int interleaved) {
+    constexpr int NW = GATED ? 2 : 1;
+    constexpr int kStageElems = (1 + NW) * kET * kELD;
+    extern __shared__ __align__(16) unsigned char moe_smem[];
+    __nv_bfloat16* stages = reinterpret_cast<__nv_bfloat16*>(moe_smem);
     __shared__ long long arow[kET];
     pdl_launch_dependents();
     pdl_wait();
@@ -167,32 +179,33 @@ moe_gemm_tc_kernel(const __nv_bfloat16* __restrict__ A, long long lda, const int
     const int n0 = blockIdx.x * kET;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const __nv_bfloat16* We = W + static_cast<long long>(e) * expert_stride;
+    const long long g_base = (GATED && interleaved) ? 2ll * n0 : n0;          // matrix row of the tile's first gate output
+    const long long u_base = (GATED && interleaved) ? 2ll * n0 + 64 : static_cast<long long>(N) + n0;
     if (threadIdx.x < kET) {
         const int p = p0 + threadIdx.x;
         arow[threadIdx.x] = threadIdx.x < rows ? static_cast<long long>(gather ? perm[p] / top : p) * lda : -1;
     }
     __syncthreads();
-    float acc[GATED ? 2 : 1][kET / 8][4];
+    float acc[NW][kET / 8][4];
 #pragma unroll
-    for (int g = 0; g < (GATED ? 2 : 1); ++g)
+    for (int g = 0; g < NW; ++g)
 #pragma unroll
         for (int i = 0; i < kET / 8; ++i) acc[g][i][0] = acc[g][i][1] = acc[g][i][2] = acc[g][i][3] = 0.f;
     const bool vec = (K & 7) == 0 && ((lda | ldw | expert_stride) & 7) == 0 &&
                      ((reinterpret_cast<unsigned long long>(A) | reinterpret_cast<unsigned long long>(W)) & 15) == 0;
-    for (int k0 = 0; k0 < K; k0 += kEK) {
+    const int nk = (K + kEK - 1) / kEK;
+    auto load = [&](int kc, int stage) {
+        __nv_bfloat16* sa = stages + stage * kStageElems;
+        __nv_bfloat16* sw = sa + kET * kELD;
+        const int k0 = kc * kEK;
         if (vec) {
             for (int c = threadIdx.x; c < kET * (kEK / 8); c += 128) {
                 const int r = c / (kEK / 8), k8 = (c - r * (kEK / 8)) * 8;
                 const int k = k0 + k8, n = n0 + r;
-                uint4 av = make_uint4(0, 0, 0, 0), wv = av, uv = av;
-                if (arow[r] >= 0 && k < K) av = *reinterpret_cast<const uint4*>(A + arow[r] + k);
-                if (n < N && k < K) {
-                    wv = __ldg(reinterpret_cast<const uint4*>(We + static_cast<long long>(n) * ldw + k));
-                    if (GATED) uv = __ldg(reinterpret_cast<const uint4*>(We + static_cast<long long>(N + n) * ldw + k));
-                }
-                *reinterpret_cast<uint4*>(sa + r * kELD + k8) = av;
-                *reinterpret_cast<uint4*>(sw + r * kELD + k8) = wv;
-                if (GATED) *reinterpret_cast<uint4*>(sw + (kET + r) * kELD + k8) = uv;
+                const bool a_ok = arow[r] >= 0 && k < K, w_ok = n < N && k < K;
+                moe_cp16(sa + r * kELD + k8, A + (a_ok ? arow[r] + k : 0), a_ok);
+                moe_cp16(sw + r * kELD + k8, We + (w_ok ? (g_base + r) * ldw + k : 0), w_ok);
+                if (GATED) moe_cp16(sw + (kET + r) * kELD + k8, We + (w_ok ? (u_base + r) * ldw + k : 0), w_ok);
             }
         } else {
             const __nv_bfloat16 zero = __float2bfloat16_rn(0.f);
@@ -200,18 +213,30 @@ moe_gemm_tc_kernel(const __nv_bfloat16* __restrict__ A, long long lda, const int
                 const int r = c / kEK, kk = c - r * kEK;
                 const int k = k0 + kk, n = n0 + r;
                 sa[r * kELD + kk] = (arow[r] >= 0 && k < K) ? A[arow[r] + k] : zero;
-                sw[r * kELD + kk] = (n < N && k < K) ? We[static_cast<long long>(n) * ldw + k] : zero;
-                if (GATED) sw[(kET + r) * kELD + kk] = (n < N && k < K) ? We[static_cast<long long>(N + n) * ldw + k] : zero;
+                sw[r * kELD + kk] = (n < N && k < K) ? We[(g_base + r) * ldw + k] : zero;
+                if (GATED) sw[(kET + r) * kELD + kk] = (n < N && k < K) ? We[(u_base + r) * ldw + k] : zero;
             }
         }
-        __syncthreads();
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    };
+    for (int s = 0; s < kEStages - 1; ++s) {
+        if (s < nk) load(s, s);
+        else asm volatile("cp.async.commit_group;" ::: "memory");
+    }
+    for (int kc = 0; kc < nk; ++kc) {
+        asm volatile("cp.async.wait_group %0;" ::"n"(kEStages - 2) : "memory");
+        __syncthreads();   // chunk kc has landed for every thread, and the stage chunk kc - 1 used is free
+        if (kc + kEStages - 1 < nk) load(kc + kEStages - 1, (kc + kEStages - 1) % kEStages);
+        else asm volatile("cp.async.commit_group;" ::: "memory");
+        const __nv_bfloat16* sa = stages + (kc % kEStages) * kStageElems;
+        const __nv_bfloat16* sw = sa + kET * kELD;
         if (warp * 16 < rows) {
 #pragma unroll
             for (int ks = 0; ks < kEK / 16; ++ks) {
                 uint32_t a[4];
                 ldsm_x4(smem_u32(sa + (warp * 16 + (lane & 15)) * kELD + ks * 16 + (lane >> 4) * 8), a[0], a[1], a[2], a[3]);
 #pragma unroll
-                for (int g = 0; g < (GATED ? 2 : 1); ++g) {
+                for (int g = 0; g < NW; ++g) {
 #pragma unroll
                     for (int nb2 = 0; nb2 < kET / 16; ++nb2) {
                         uint32_t b0, b1, b2, b3;
@@ -223,8 +248,8 @@ moe_gemm_tc_kernel(const __nv_bfloat16* __restrict__ A, long long lda, const int
                 }
             }
         }
-        __syncthreads();
     }
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
 #pragma unroll
     for (int rr = 0; rr < 2; ++rr) {
         const int r = warp * 16 + (lane >> 2) + 8 * rr;
@@ -237,7 +262,7 @@ moe_gemm_tc_kernel(const __nv_bfloat16* __restrict__ A, long long lda, const int
                 const int n = n0 + nb * 8 + (lane & 3) * 2 + q;
                 if (n >= N) continue;
                 if (GATED) {
-                    const float g = acc[0][nb][2 * rr + q], u = acc[GATED ? 1 : 0][nb][2 * rr + q];
+                    const float g = acc[0][nb][2 * rr + q], u = acc[NW - 1][nb][2 * rr + q];
                     reinterpret_cast<__nv_bfloat16*>(out)[p * ldo + n] = __float2bfloat16_rn(g / (1.f + expf(-g)) * u);
                 } else {
                     reinterpret_cast<float*>(out)[p * ldo + n] = acc[0][nb][2 * rr + q];
@@ -252,7 +277,7 @@ template <typename XT, bool GATED>
 __global__ void __launch_bounds__(256)
 moe_gemm_fma_kernel(const XT* __restrict__ A, long long lda, const int* __restrict__ perm, int top, int gather,
                     const XT* __restrict__ W, long long expert_stride, long long ldw, void* __restrict__ out, long long ldo,
-                    int N, int K, const int* __restrict__ seg_off, const int* __restrict__ tiles) {
+                    int N, int K, const int* __restrict__ seg_off, const int* __restrict__ tiles, int interleaved) {
     constexpr int KC = 16;
     __shared__ float sa[KC][kET + 1];
     __shared__ float sw[GATED ? 2 : 1][KC][kET + 1];
@@ -265,6 +290,8 @@ moe_gemm_fma_kernel(const XT* __restrict__ A, long long lda, const int* __restri
     const int n0 = blockIdx.x * kET;
     const int tx = threadIdx.x % 16, ty = threadIdx.x / 16;
     const XT* We = W + static_cast<long long>(e) * expert_stride;
+    const long long g_base = (GATED && interleaved) ? 2ll * n0 : n0;
+    const long long u_base = (GATED && interleaved) ? 2ll * n0 + 64 : static_cast<long long>(N) + n0;
     if (threadIdx.x < kET) {
         const int p = p0 + threadIdx.x;
         arow[threadIdx.x] = static_cast<int>(threadIdx.x) < rows ? static_cast<long long>(gather ? perm[p] / top : p) * lda : -1;
@@ -282,8 +309,8 @@ moe_gemm_fma_kernel(const XT* __restrict__ A, long long lda, const int* __restri
             const int r = c / KC, kk = c - r * KC;
             const int k = k0 + kk, n = n0 + r;
             sa[kk][r] = (arow[r] >= 0 && k < K) ? mld(A, arow[r] + k) : 0.f;
-            sw[0][kk][r] = (n < N && k < K) ? mld(We, static_cast<long long>(n) * ldw + k) : 0.f;
-            if (GATED) sw[GATED ? 1 : 0][kk][r] = (n < N && k < K) ? mld(We, static_cast<long long>(N + n) * ldw + k) : 0.f;
+            sw[0][kk][r] = (n < N && k < K) ? mld(We, (g_base + r) * ldw + k) : 0.f;
+            if (GATED) sw[GATED ? 1 : 0][kk][r] = (n < N && k < K) ? mld(We, (u_base + r) * ldw + k) : 0.f;
         }
         __syncthreads();
 #pragma unroll
@@ -384,10 +411,12 @@ int atx_moe_plan(const int* sel, int n_pairs, int E, int* seg_off, int* perm, in
 
 int atx_moe_expert_gemm(const void* A, long long lda, const int* perm, int top, int gather, const void* W,
                         long long expert_stride, long long ldw, void* out, long long ldo, int N, int K, int gated,
-                        const int* seg_off, const int* tiles, int max_tiles, int dtype, int flags, atx_stream_t stream) {
+                        int interleaved, const int* seg_off, const int* tiles, int max_tiles, int dtype, int flags,
+                        atx_stream_t stream) {
     ATX_REQUIRE(A && W && out && seg_off && tiles && (!gather || perm), "atx_moe_expert_gemm: null pointer");
     ATX_REQUIRE(N > 0 && K > 0 && max_tiles > 0 && max_tiles <= 65535 && top > 0 && ldw >= K && lda >= K && ldo >= N,
                 "atx_moe_expert_gemm: bad shape N=%d K=%d tiles=%d lda=%lld ldw=%lld ldo=%lld", N, K, max_tiles, lda, ldw, ldo);
+    ATX_REQUIRE(!interleaved || (gated && N % 64 == 0), "atx_moe_expert_gemm: interleaved gate / up rows need N %% 64 == 0");
     cudaLaunchConfig_t cfg = {};
     cudaLaunchAttribute attr[1];
     cfg.gridDim = dim3((N + kET - 1) / kET, max_tiles);
@@ -395,9 +424,20 @@ int atx_moe_expert_gemm(const void* A, long long lda, const int* perm, int top, 
     set_pdl_moe(cfg, attr, flags);
 #define ATX_MOE_LAUNCH(KERNEL_, T_)                                                                                     \
     ATX_CUDA(cudaLaunchKernelEx(&cfg, KERNEL_, reinterpret_cast<const T_*>(A), lda, perm, top, gather,                \
-                                reinterpret_cast<const T_*>(W), expert_stride, ldw, out, ldo, N, K, seg_off, tiles))
+                                reinterpret_cast<const T_*>(W), expert_stride, ldw, out, ldo, N, K, seg_off, tiles,  \
+                                interleaved))
     if (dtype == ATX_DT_BF16) {
         cfg.blockDim = dim3(128);
+        const int smem = kEStages * ((gated ? 3 : 2) * kET * kELD) * 2;
+        cfg.dynamicSmemBytes = smem;
+        static bool attr_done[2] = {false, false};
+        if (!attr_done[gated ? 1 : 0]) {
+            if (gated)
+                ATX_CUDA(cudaFuncSetAttribute(moe_gemm_tc_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+            else
+                ATX_CUDA(cudaFuncSetAttribute(moe_gemm_tc_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+            attr_done[gated ? 1 : 0] = true;
+        }
         if (gated)
             ATX_MOE_LAUNCH(moe_gemm_tc_kernel<true>, __nv_bfloat16);
         else

@@ -515,7 +515,9 @@ def routed_trace_measure(world: int, device_ecfg, model: str = "random:8b:0") ->
 
 # ------------------------------------------------------------------------------------------------------
 def safisun_measure(args, local, pk, family: str = "safisun") -> dict:
-    """`--workload safisun | gopopel`: prefill and decode throughput of a layer-list family (Safisun: state-space,
+    """`--workload safisun | gopopel | zonidra`: prefill and decode throughput of a layer-list family (Zonidra: sigmoid
+    attention under a window with kept first keys, token shift, dense and expert feed-forwards, beside the Gopopel and the
+    Llama shape; Safisun: state-space,
     linear-attention and block-local attention mixers; Gopopel: parallel layers of latent attention and windowed
     attention) at shapes with the width, depth, feed-forward size and vocabulary of Llama shapes, each beside that Llama
     shape (Gopopel also beside the Safisun shape) through the same engine: B prompts of P random tokens (chunked prefill,
@@ -533,7 +535,7 @@ def safisun_measure(args, local, pk, family: str = "safisun") -> dict:
     B, P, O = args.arch_batch, args.arch_prompt, args.arch_out
     records, launches = [], 0
     for size in [x for x in args.arch_sizes.split(",") if x]:
-        beside = (f"random:safisun-{size}:0",) if family != "safisun" else ()
+        beside = {"safisun": (), "gopopel": (f"random:safisun-{size}:0",), "zonidra": (f"random:gopopel-{size}:0",)}[family]
         for model in (f"random:{family}-{size}:0",) + beside + (f"random:{size}:0",):
             src = resolve_model(model)
             ecfg = EngineConfig(max_model_len=P + O + 16, max_num_seqs=B, max_num_batched_tokens=8192,
@@ -562,12 +564,17 @@ def safisun_measure(args, local, pk, family: str = "safisun") -> dict:
             pf = [(a.elapsed_time(b), npf) for (a, b, nd, npf, ctx) in evs if npf > 0]
             ms = statistics.median(dec)
             pf_ms, pf_tok = sum(x[0] for x in pf), sum(x[1] for x in pf)
-            wbytes = mcfg.weight_bytes_per_decode_step()
+            try:      # a mixture of experts streams only the experts the step's tokens chose
+                wbytes = mcfg.weight_bytes_per_decode_step(2, B)
+            except TypeError:
+                wbytes = mcfg.weight_bytes_per_decode_step()
             state = getattr(mcfg, "state_bytes_per_sequence", lambda: 0)()
             if hasattr(mcfg, "decode_kv_bytes"):      # windowed attention reads at most its window
                 byts = wbytes + mcfg.decode_kv_bytes(P + O // 2) * B
             else:
                 byts = wbytes + 2 * state * B + mcfg.kv_bytes_per_token() * B * (P + O // 2) * (0 if state else 1)
+            if hasattr(mcfg, "decode_kv_bytes"):
+                byts += 2 * state * B
             records.append({"model": model, "params_bytes": wbytes, "layers": mcfg.num_hidden_layers,
                             "prefill_tokens_per_s": round(pf_tok / pf_ms * 1e3), "prefill_ms_per_8192_tokens":
                             round(pf_ms / pf_tok * 8192, 2),
@@ -702,7 +709,7 @@ def run_other_workload(args, rank, world, local):
                     "config": {"workload": f"BASELINE configs[4]: Llama-3.1-8B long-context, batch {B} x {P}-token prompts "
                                            f"(chunked prefill, 8192-token budget) + {O} greedy tokens over paged KV",
                                "parallelism": "1 GPU", "kv_blocks": r.num_blocks}})
-    elif args.workload in ("safisun", "gopopel"):
+    elif args.workload in ("safisun", "gopopel", "zonidra"):
         out.update(safisun_measure(args, local, pk, args.workload))
         if rank == 0:
             print(json.dumps(out), flush=True)
@@ -737,12 +744,12 @@ def main() -> None:
     ap.add_argument("--no-multi", action="store_true", help="N > 1: skip the routed-DP and 70B-TP records")
     ap.add_argument("--tp70b-any-n", action="store_true", help="attach the 70B tensor-parallel record at any N > 1 "
                                                                "(default: only at N = 8, BASELINE configs[3])")
-    ap.add_argument("--arch-sizes", default="1b,8b", help="--workload safisun | gopopel: shapes to run (each beside the Llama shape "
+    ap.add_argument("--arch-sizes", default="1b,8b", help="--workload safisun | gopopel | zonidra: shapes to run (each beside the Llama shape "
                                                           "of the same width, depth, feed-forward and vocabulary)")
     ap.add_argument("--arch-batch", type=int, default=8)
     ap.add_argument("--arch-prompt", type=int, default=2048)
     ap.add_argument("--arch-out", type=int, default=64)
-    ap.add_argument("--workload", default="fanout", choices=["fanout", "trace", "long", "tp70b", "safisun", "gopopel"],
+    ap.add_argument("--workload", default="fanout", choices=["fanout", "trace", "long", "tp70b", "safisun", "gopopel", "zonidra"],
                     help="fanout = headline BASELINE configs[1] (default); the others are configs[2..4]")
     ap.add_argument("--trace-out", default="", help="directory for response.json / llm_calls.jsonl of a trace replay")
     ap.add_argument("--long-out", type=int, default=128)

@@ -702,7 +702,7 @@ def test_polynomial_norm_activation_and_scaled_residual_norm(F):
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("E,ident,top,Fe,W,T", [(5, 2, 3, 24, 64, 150), (1, 0, 1, 8, 40, 7), (40, 3, 6, 16, 72, 130),
-                                               (3, 4, 7, 64, 128, 65)])
+                                               (3, 4, 7, 64, 128, 65), (6, 0, 2, 128, 192, 300)])
 def test_expert_mixture_kernels_route_sort_multiply_and_sum(E, ident, top, Fe, W, T, dtype):
     """Router logits built so that the choice differs from the plain arg-max (the correction decides) and the weight is
     the uncorrected score; every expert's rows go through its own matrices; identity choices return the input."""
@@ -738,14 +738,19 @@ def test_expert_mixture_kernels_route_sort_multiply_and_sum(E, ident, top, Fe, W
     seg, perm, slot_of = (torch.zeros(n, dtype=i32, device=DEV) for n in (E + 1, T * top, T * top))
     tiles = torch.zeros(2 + 2 * max_tiles, dtype=i32, device=DEV)
     ck(L.atx_moe_plan(sel.data_ptr(), T * top, E, seg.data_ptr(), perm.data_ptr(), slot_of.data_ptr(), tiles.data_ptr(), 0, stream()))
-    w_gu = dev(torch.stack([torch.cat([wt[f"e{e}.gate"], wt[f"e{e}.up"]]) for e in range(E)]), xt)
+    inter = 1 if (dtype == "bfloat16" and Fe % 64 == 0) else 0      # gate / up rows in blocks of 64, or gate rows then up rows
+    if inter:
+        w_gu = dev(torch.stack([torch.stack((wt[f"e{e}.gate"].view(Fe // 64, 64, W), wt[f"e{e}.up"].view(Fe // 64, 64, W)), 1)
+                                .reshape(2 * Fe, W) for e in range(E)]), xt)
+    else:
+        w_gu = dev(torch.stack([torch.cat([wt[f"e{e}.gate"], wt[f"e{e}.up"]]) for e in range(E)]), xt)
     w_dn = dev(torch.stack([wt[f"e{e}.down"] for e in range(E)]), xt)
     ud = dev(u)
     eact = torch.zeros(T * top, Fe, dtype=xt, device=DEV)
     ye = torch.zeros(T * top, W, device=DEV)
     ck(L.atx_moe_expert_gemm(ud.data_ptr(), W, perm.data_ptr(), top, 1, w_gu.data_ptr(), 2 * Fe * W, W, eact.data_ptr(), Fe, Fe, W,
-                             1, seg.data_ptr(), tiles.data_ptr(), max_tiles, dt, 0, stream()))
-    ck(L.atx_moe_expert_gemm(eact.data_ptr(), Fe, None, top, 0, w_dn.data_ptr(), W * Fe, Fe, ye.data_ptr(), W, W, Fe, 0,
+                             1, inter, seg.data_ptr(), tiles.data_ptr(), max_tiles, dt, 0, stream()))
+    ck(L.atx_moe_expert_gemm(eact.data_ptr(), Fe, None, top, 0, w_dn.data_ptr(), W * Fe, Fe, ye.data_ptr(), W, W, Fe, 0, 0,
                              seg.data_ptr(), tiles.data_ptr(), max_tiles, dt, 0, stream()))
     y = dev(ysh)
     ck(L.atx_moe_combine(y.data_ptr(), ye.data_ptr(), W, ud.data_ptr(), sel.data_ptr(), wg.data_ptr(), slot_of.data_ptr(),
