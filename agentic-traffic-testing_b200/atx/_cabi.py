@@ -44,7 +44,8 @@ EXPORTS = [
     "atx_attn_window_decode", "atx_attn_window_decode_supported", "atx_attn_window_decode_workspace_bytes",
     "atx_resid_norm_scaled", "atx_embed_rows_pair", "atx_token_shift", "atx_poly_norm_act",
     "atx_attn_paged", "atx_attn_paged_prefill", "atx_attn_paged_decode",
-    "atx_moe_route", "atx_moe_tile_rows", "atx_moe_plan", "atx_moe_expert_gemm", "atx_moe_combine",
+    "atx_moe_route", "atx_moe_tile_rows", "atx_moe_plan", "atx_moe_expert_gemm", "atx_moe_combine", "atx_moe_gather_rows",
+    "atx_gemm_run_grouped", "atx_gemm_grouped_tile_rows",
 ]
 ATTN_SOFTMAX = 0
 ATTN_SIGMOID = 1
@@ -185,7 +186,10 @@ def load() -> C.CDLL:
                                           i32, i32, i32, i32, po, i32, i32, vp]
     lib.atx_moe_route.argtypes = [vp, i64, vp, i32, i32, f32, vp, vp, i32, i32, vp]
     lib.atx_moe_tile_rows.argtypes = []
-    lib.atx_moe_plan.argtypes = [vp, i32, i32, vp, vp, vp, vp, i32, vp]
+    lib.atx_moe_plan.argtypes = [vp, i32, i32, i32, vp, vp, vp, vp, i32, vp]
+    lib.atx_moe_gather_rows.argtypes = [vp, i64, vp, i32, vp, i32, vp, i64, i32, i32, i32, i32, vp]
+    lib.atx_gemm_run_grouped.argtypes = [vp, vp, i64, i32, i32, vp, vp, i32, i32, vp]
+    lib.atx_gemm_grouped_tile_rows.argtypes = []
     lib.atx_moe_expert_gemm.argtypes = [vp, i64, vp, i32, i32, vp, i64, i64, vp, i64, i32, i32, i32, i32, vp, vp, i32, i32, i32, vp]
     lib.atx_moe_combine.argtypes = [vp, vp, i64, vp, vp, vp, vp, vp, i64, i32, i32, i32, i32, i32, i32, vp]
     for name in EXPORTS:  # fail at load time, not at first use, if the build is stale

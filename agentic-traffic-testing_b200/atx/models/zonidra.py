@@ -434,6 +434,12 @@ class Program:
         self.slot_of = torch.zeros(P, dtype=i32, device=dev)
         self.tiles = torch.zeros(2 + 2 * self.max_tiles, dtype=i32, device=dev)
         self.eact = torch.zeros(P * n_ef if n_exp > 1 or n_ef > 1 else 1, dtype=xt, device=dev)
+        # prompt-sized steps on the tcgen05 GEMM: every expert's input rows back to back, tiles of its own row count
+        self.big_rows = int(lib.atx_gemm_grouped_tile_rows())
+        self.max_big_tiles = (P + self.big_rows - 1) // self.big_rows + n_exp
+        grouped = any(l.egu_interleaved for l in w.layers)
+        self.xperm = torch.zeros(P if grouped else 1, W, dtype=xt, device=dev)
+        self.tiles_big = torch.zeros(2 + 2 * self.max_big_tiles, dtype=i32, device=dev)
         self.ye = torch.zeros(P * W if n_ef > 1 else 1, dtype=f32, device=dev)
         self._views: Dict[Tuple[int, int], torch.Tensor] = {}
 
@@ -453,6 +459,10 @@ class Program:
                 d["down"] = _Linear(lib, l.w_down, view(self.act_flat, l.w_down.shape[1]), self.dt)
             elif l.ff == "moe":
                 d["router"] = _Linear(lib, l.w_router, self.xn, self.dt)
+                if l.egu_interleaved:
+                    E_, F2, Fe_ = l.w_egu.shape[0], l.w_egu.shape[1], l.w_edown.shape[2]
+                    d["egu"] = _cabi.GemmPlan(l.w_egu.view(E_ * F2, W), self.xperm)
+                    d["edown"] = _cabi.GemmPlan(l.w_edown.view(E_ * W, Fe_), self.eact[:P * Fe_].view(P, Fe_))
                 if l.w_sgu is not None:
                     d["sgu"] = _Linear(lib, l.w_sgu, self.xn, self.dt)
                     d["sdown"] = _Linear(lib, l.w_sdown, view(self.act_flat, l.w_sdown.shape[1]), self.dt)
@@ -636,15 +646,24 @@ class Program:
                 lin["router"].run(rl, Rn, T, fl, st, zeroed=acc)
                 ck(lib.atx_moe_route(rl, Rn, l.correction.data_ptr(), R, top, float(rt.get("scale", 1.0)), self.sel.data_ptr(),
                                      self.wgt.data_ptr(), T, fl, st))
-                ck(lib.atx_moe_plan(self.sel.data_ptr(), T * top, E, self.seg_off.data_ptr(), self.perm.data_ptr(),
-                                    self.slot_of.data_ptr(), self.tiles.data_ptr(), fl, st))
-                tiles = min(self.max_tiles, (T * top + self.tile_rows - 1) // self.tile_rows + E)
-                ck(lib.atx_moe_expert_gemm(xn, W, self.perm.data_ptr(), top, 1, l.w_egu.data_ptr(), 2 * Fe * W, W,
-                                           self.eact.data_ptr(), Fe, Fe, W, 1, 1 if l.egu_interleaved else 0,
-                                           self.seg_off.data_ptr(), self.tiles.data_ptr(), tiles, dt, fl, st))
-                ck(lib.atx_moe_expert_gemm(self.eact.data_ptr(), Fe, None, top, 0, l.w_edown.data_ptr(), W * Fe, Fe,
-                                           self.ye.data_ptr(), W, W, Fe, 0, 0, self.seg_off.data_ptr(), self.tiles.data_ptr(),
-                                           tiles, dt, fl, st))
+                pairs, so, pm, sl = T * top, self.seg_off.data_ptr(), self.perm.data_ptr(), self.slot_of.data_ptr()
+                if "egu" in lin and not small:
+                    # prompt-sized: gather every expert's rows, then both products on the tcgen05 GEMM over the plan's tiles
+                    big, tb = min(self.max_big_tiles, (pairs + self.big_rows - 1) // self.big_rows + E), self.tiles_big.data_ptr()
+                    ck(lib.atx_moe_plan(self.sel.data_ptr(), pairs, E, self.big_rows, so, pm, sl, tb, fl, st))
+                    ck(lib.atx_moe_gather_rows(xn, W, pm, top, so, E, self.xperm.data_ptr(), W, pairs, W, dt, fl, st))
+                    ck(lib.atx_gemm_run_grouped(lin["egu"]._h, self.eact.data_ptr(), Fe, 2 * Fe, _cabi.GEMM_SWIGLU_BF16, so, tb,
+                                                big, fl, st))
+                    ck(lib.atx_gemm_run_grouped(lin["edown"]._h, self.ye.data_ptr(), W, W, _cabi.GEMM_STORE_F32, so, tb, big, fl,
+                                                st))
+                    n += 1
+                else:
+                    tiles, tl = min(self.max_tiles, (pairs + self.tile_rows - 1) // self.tile_rows + E), self.tiles.data_ptr()
+                    ck(lib.atx_moe_plan(self.sel.data_ptr(), pairs, E, self.tile_rows, so, pm, sl, tl, fl, st))
+                    ck(lib.atx_moe_expert_gemm(xn, W, pm, top, 1, l.w_egu.data_ptr(), 2 * Fe * W, W, self.eact.data_ptr(), Fe, Fe,
+                                               W, 1, 1 if l.egu_interleaved else 0, so, tl, tiles, dt, fl, st))
+                    ck(lib.atx_moe_expert_gemm(self.eact.data_ptr(), Fe, None, top, 0, l.w_edown.data_ptr(), W * Fe, Fe,
+                                               self.ye.data_ptr(), W, W, Fe, 0, 0, so, tl, tiles, dt, fl, st))
                 n += 5
                 if shared:
                     if l.sgu_interleaved:

@@ -121,9 +121,11 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
         : "memory");
     return ok != 0;
 }
+// Bounded: a wait that nothing will ever satisfy (a protocol fault) ends after about a second of polling instead of holding
+// the GPU; the kernel then runs on to its end, frees what it holds, and its result is wrong rather than missing.
 __device__ __forceinline__ void mbar_wait(uint64_t* bar, uint32_t parity) {
-    while (!mbar_try_wait(bar, parity)) {
-    }
+    for (uint32_t i = 0; i < (1u << 26); ++i)
+        if (mbar_try_wait(bar, parity)) return;
 }
 
 // ---- TMA -------------------------------------------------------------------------------------------

@@ -365,7 +365,8 @@ template <int TN>
 __global__ void __launch_bounds__(kPersistThreads, 1)
 gemm_wt_persistent_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmX,
                           void* __restrict__ out, long long ldo, int T, int N, int kb_total, int tiles_t,
-                          int total_tiles, int mode, int w_evict_first) {
+                          int total_tiles, int mode, int w_evict_first, const int* __restrict__ grp_tiles,
+                          const int* __restrict__ grp_seg, int grp_w_rows) {
     using Cfg = PersistCfg<TN>;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
@@ -408,13 +409,26 @@ gemm_wt_persistent_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_
             int stage = 0;
             uint32_t phase = 0;
             bool waited = false;
-            for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x) {
-                const int n0 = (tile / tiles_t) * kBM, t0 = (tile % tiles_t) * TN;
+            int tot = total_tiles, tt = tiles_t;
+            if (grp_tiles) {   // the tile list is the upstream kernels' work
+                pdl_wait();
+                waited = true;
+                tt = grp_tiles[0];
+                tot = tt * ((N + kBM - 1) / kBM);
+            }
+            for (int tile = blockIdx.x; tile < tot; tile += gridDim.x) {
+                const int n0 = (tile / tt) * kBM;
+                int t0 = (tile % tt) * TN, w_row = n0;
+                if (grp_tiles) {
+                    const int ti = tile % tt;
+                    t0 = grp_tiles[3 + 2 * ti];
+                    w_row = grp_tiles[2 + 2 * ti] * grp_w_rows + n0;
+                }
                 for (int kb = 0; kb < kb_total; ++kb) {
                     mbar_wait(&empty_bar[stage], phase ^ 1);
                     uint8_t* st = smem + stage * Cfg::kStageBytes;
                     mbar_expect_tx(&full_bar[stage], Cfg::kStageBytes);
-                    tma_load_2d(st, &tmW, &full_bar[stage], kb * kBK, n0, polW);
+                    tma_load_2d(st, &tmW, &full_bar[stage], kb * kBK, w_row, polW);
                     if (!waited) {  // weights never depend on the upstream kernel, activations do
                         pdl_wait();
                         waited = true;
@@ -433,7 +447,12 @@ gemm_wt_persistent_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_
             constexpr uint32_t idesc = umma_idesc_bf16(kBM, TN);
             int stage = 0, acc = 0;
             uint32_t phase = 0, acc_phase = 0;
-            for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x) {
+            int tot = total_tiles;
+            if (grp_tiles) {
+                pdl_wait();
+                tot = grp_tiles[0] * ((N + kBM - 1) / kBM);
+            }
+            for (int tile = blockIdx.x; tile < tot; tile += gridDim.x) {
                 mbar_wait(&tmem_empty[acc], acc_phase ^ 1);  // epilogue has drained this accumulator
                 tc_fence_after();
                 const uint32_t d_tmem = tmem_base + acc * TN;
@@ -467,8 +486,21 @@ gemm_wt_persistent_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_
         int acc = 0;
         uint32_t acc_phase = 0;
         bool waited = false;
-        for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x) {
-            const int n0 = (tile / tiles_t) * kBM, t0 = (tile % tiles_t) * TN;
+        int tot = total_tiles, tt = tiles_t;
+        if (grp_tiles) {
+            pdl_wait();
+            waited = true;
+            tt = grp_tiles[0];
+            tot = tt * ((N + kBM - 1) / kBM);
+        }
+        for (int tile = blockIdx.x; tile < tot; tile += gridDim.x) {
+            const int n0 = (tile / tt) * kBM;
+            int t0 = (tile % tt) * TN, t_end = T;   // rows [t0, t_end) of this tile are stored
+            if (grp_tiles) {
+                const int ti = tile % tt;
+                t0 = grp_tiles[3 + 2 * ti];
+                t_end = grp_seg[grp_tiles[2 + 2 * ti] + 1];
+            }
             mbar_wait(&tmem_full[acc], acc_phase);
             tc_fence_after();
             if (!waited) {  // `out` may be the residual stream written by the upstream grid
@@ -480,7 +512,7 @@ gemm_wt_persistent_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_
                 // symmetric exchange in groups of 32 token columns: gate warps finish columns [0, TN/2),
                 // up warps columns [TN/2, TN); each parks the half the other pair needs
                 constexpr int HALF = TN / 2;
-                const long long col = static_cast<long long>(tile / tiles_t) * 64 + feat;
+                const long long col = static_cast<long long>(tile / tt) * 64 + feat;
                 const bool ok = col < N / 2;
                 __nv_bfloat16* o = reinterpret_cast<__nv_bfloat16*>(out);
                 float* park_mine = xchg + (gate_warp ? 0 : 32 * 64);    // [32][64] floats each
@@ -508,7 +540,7 @@ gemm_wt_persistent_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_
                             const int t = t0 + c_own + c + j;
                             const float mine = __uint_as_float(v[j]), other = park_other[(c + j) * 64 + feat];
                             const float gg = gate_warp ? mine : other, uu = gate_warp ? other : mine;
-                            if (ok && t < T)
+                            if (ok && t < t_end)
                                 o[static_cast<long long>(t) * ldo + col] =
                                     __float2bfloat16_rn(gg / (1.f + expf(-gg)) * uu);
                         }
@@ -520,7 +552,7 @@ gemm_wt_persistent_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_
                 const bool n_ok = n < N;
 #pragma unroll 1
                 for (int c = 0; c < TN; c += 16) {
-                    if (t0 + c >= T) break;
+                    if (t0 + c >= t_end) break;
                     uint32_t v[16];
                     tmem_ld16(tlane + c, v);
                     tmem_ld_wait();
@@ -530,14 +562,14 @@ gemm_wt_persistent_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_
 #pragma unroll
                             for (int j = 0; j < 16; ++j) {
                                 const int t = t0 + c + j;
-                                if (t < T) o[static_cast<long long>(t) * ldo + n] = __uint_as_float(v[j]);
+                                if (t < t_end) o[static_cast<long long>(t) * ldo + n] = __uint_as_float(v[j]);
                             }
                         } else if (mode == ATX_GEMM_ADD_F32) {
                             float* o = reinterpret_cast<float*>(out);
 #pragma unroll
                             for (int j = 0; j < 16; ++j) {
                                 const int t = t0 + c + j;
-                                if (t < T) atomicAdd(o + static_cast<long long>(t) * ldo + n, __uint_as_float(v[j]));
+                                if (t < t_end) atomicAdd(o + static_cast<long long>(t) * ldo + n, __uint_as_float(v[j]));
                             }
                         } else {
                             __nv_bfloat16* o = reinterpret_cast<__nv_bfloat16*>(out);
@@ -550,7 +582,7 @@ gemm_wt_persistent_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_
                                     a = fmaxf(a, 0.f);
                                     a *= a;
                                 }
-                                if (t < T) o[static_cast<long long>(t) * ldo + n] = __float2bfloat16_rn(a);
+                                if (t < t_end) o[static_cast<long long>(t) * ldo + n] = __float2bfloat16_rn(a);
                             }
                         }
                     }
@@ -708,7 +740,39 @@ static int launch_gemm_persistent(const atx_gemm_plan* p, int ti, void* out, lon
     cfg.attrs = attr;
     cfg.numAttrs = pdl ? 1 : 0;
     ATX_CUDA(cudaLaunchKernelEx(&cfg, gemm_wt_persistent_kernel<TN>, p->tmW, p->tmX[ti], out, ldo, T,
-                                static_cast<int>(p->N), kb_total, tiles_t, total, mode, p->w_evict_first));
+                                static_cast<int>(p->N), kb_total, tiles_t, total, mode, p->w_evict_first,
+                                static_cast<const int*>(nullptr), static_cast<const int*>(nullptr), 0));
+    return ATX_OK;
+}
+
+// The persistent kernel over a device-side list of row tiles, each with its own block of W rows (one expert's matrix):
+// the grid is sized for the most tiles the list can hold; CTAs find the real count in the list.
+template <int TN>
+static int launch_gemm_grouped(const atx_gemm_plan* p, int ti, void* out, long long ldo, int n_group, int mode,
+                               const int* seg, const int* tiles, int max_row_tiles, int pdl, cudaStream_t stream) {
+    using Cfg = PersistCfg<TN>;
+    static bool attr_done[64] = {false};
+    int dev = 0;
+    ATX_CUDA(cudaGetDevice(&dev));
+    if (dev >= 0 && dev < 64 && !attr_done[dev]) {
+        ATX_CUDA(cudaFuncSetAttribute(gemm_wt_persistent_kernel<TN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                      Cfg::kSmemBytes));
+        attr_done[dev] = true;
+    }
+    const int kb_total = static_cast<int>(p->K / kBK);
+    const long long most = static_cast<long long>((n_group + kBM - 1) / kBM) * max_row_tiles;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(static_cast<unsigned>(most < num_sms() ? most : num_sms()));
+    cfg.blockDim = dim3(kPersistThreads);
+    cfg.dynamicSmemBytes = Cfg::kSmemBytes;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = pdl ? 1 : 0;
+    ATX_CUDA(cudaLaunchKernelEx(&cfg, gemm_wt_persistent_kernel<TN>, p->tmW, p->tmX[ti], out, ldo, 0, n_group, kb_total, 1,
+                                0, mode, p->w_evict_first, tiles, seg, n_group));
     return ATX_OK;
 }
 
@@ -798,6 +862,23 @@ int atx_gemm_run(const atx_gemm_plan* p, void* out, long long ldo, int T, int mo
     ATX_REQUIRE(splits == 1, "atx_gemm_run: split-K is for decode-sized steps (T <= 64); got T=%d splits=%d", T, splits);
     if (T <= 128) return launch_gemm_persistent<128>(p, 3, out, ldo, T, mode, pdl, stream);
     return launch_gemm_persistent<256>(p, 4, out, ldo, T, mode, pdl, stream);
+}
+
+int atx_gemm_grouped_tile_rows(void) { return 256; }
+
+int atx_gemm_run_grouped(const atx_gemm_plan* p, void* out, long long ldo, int n_group, int mode, const int* seg_off,
+                         const int* tiles, int max_row_tiles, int flags, atx_stream_t stream_) {
+    ATX_REQUIRE(p && out && seg_off && tiles, "atx_gemm_run_grouped: null pointer");
+    ATX_REQUIRE(n_group > 0 && p->N % n_group == 0 && max_row_tiles > 0,
+                "atx_gemm_run_grouped: W has %lld rows, not a multiple of %d per group", p->N, n_group);
+    ATX_REQUIRE(mode == ATX_GEMM_STORE_F32 || mode == ATX_GEMM_SWIGLU_BF16 || mode == ATX_GEMM_STORE_BF16 ||
+                    mode == ATX_GEMM_RELU2_BF16,
+                "atx_gemm_run_grouped: mode %d (stores only: the rows of a group are written once)", mode);
+    ATX_REQUIRE(ldo >= (mode == ATX_GEMM_SWIGLU_BF16 ? n_group / 2 : n_group), "atx_gemm_run_grouped: ldo=%lld too small", ldo);
+    ATX_REQUIRE(mode != ATX_GEMM_SWIGLU_BF16 || n_group % 128 == 0, "atx_gemm_run_grouped: SWIGLU mode needs %d %% 128 == 0",
+                n_group);
+    return launch_gemm_grouped<256>(p, 4, out, ldo, n_group, mode, seg_off, tiles, max_row_tiles, (flags & ATX_FLAG_PDL) ? 1 : 0,
+                                    reinterpret_cast<cudaStream_t>(stream_));
 }
 
 }  // extern "C"

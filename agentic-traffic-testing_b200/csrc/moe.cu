@@ -350,6 +350,28 @@ moe_gemm_fma_kernel(const XT* __restrict__ A, long long lda, const int* __restri
     }
 }
 
+// out[slot, :] = x[perm[slot] / top, :] for every slot the plan handed out: the rows of each expert back to back, so that
+// a GEMM whose operands arrive by TMA can read them as tiles.
+template <typename XT>
+__global__ void __launch_bounds__(128)
+moe_gather_rows_kernel(const XT* __restrict__ x, long long ldx, const int* __restrict__ perm, int top,
+                       const int* __restrict__ seg_off, int E, XT* __restrict__ out, long long ldo, int W) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const long long slot = blockIdx.x;
+    if (slot >= seg_off[E]) return;
+    const XT* src = x + static_cast<long long>(perm[slot] / top) * ldx;
+    XT* dst = out + slot * ldo;
+    constexpr int PER = 16 / sizeof(XT);
+    if (W % PER == 0 && ldx % PER == 0 && ldo % PER == 0 &&
+        ((reinterpret_cast<unsigned long long>(x) | reinterpret_cast<unsigned long long>(out)) & 15) == 0) {
+        for (int i = threadIdx.x; i < W / PER; i += blockDim.x)
+            reinterpret_cast<uint4*>(dst)[i] = reinterpret_cast<const uint4*>(src)[i];
+        return;
+    }
+    for (int i = threadIdx.x; i < W; i += blockDim.x) dst[i] = src[i];
+}
+
 template <typename XT>
 __global__ void __launch_bounds__(256)
 moe_combine_kernel(float* __restrict__ y, const float* __restrict__ ye, long long lde, const XT* __restrict__ x,
@@ -394,10 +416,11 @@ int atx_moe_route(const float* logits, long long ld, const float* correction, in
 
 int atx_moe_tile_rows(void) { return kET; }
 
-int atx_moe_plan(const int* sel, int n_pairs, int E, int* seg_off, int* perm, int* slot_of, int* tiles, int flags,
-                 atx_stream_t stream) {
+int atx_moe_plan(const int* sel, int n_pairs, int E, int tile_rows, int* seg_off, int* perm, int* slot_of, int* tiles,
+                 int flags, atx_stream_t stream) {
     ATX_REQUIRE(sel && seg_off && perm && slot_of && tiles, "atx_moe_plan: null pointer");
-    ATX_REQUIRE(n_pairs > 0 && E > 0 && E <= 4096, "atx_moe_plan: bad shape pairs=%d experts=%d", n_pairs, E);
+    ATX_REQUIRE(n_pairs > 0 && E > 0 && E <= 4096 && tile_rows > 0, "atx_moe_plan: bad shape pairs=%d experts=%d tile=%d",
+                n_pairs, E, tile_rows);
     cudaLaunchConfig_t cfg = {};
     cudaLaunchAttribute attr[1];
     cfg.gridDim = dim3(1);
@@ -405,7 +428,7 @@ int atx_moe_plan(const int* sel, int n_pairs, int E, int* seg_off, int* perm, in
     cfg.dynamicSmemBytes = sizeof(int) * (3 * static_cast<size_t>(E) + 1);
     cfg.stream = reinterpret_cast<cudaStream_t>(stream);
     set_pdl_moe(cfg, attr, flags);
-    ATX_CUDA(cudaLaunchKernelEx(&cfg, moe_plan_kernel, sel, n_pairs, E, kET, seg_off, perm, slot_of, tiles));
+    ATX_CUDA(cudaLaunchKernelEx(&cfg, moe_plan_kernel, sel, n_pairs, E, tile_rows, seg_off, perm, slot_of, tiles));
     return ATX_OK;
 }
 
@@ -450,6 +473,26 @@ int atx_moe_expert_gemm(const void* A, long long lda, const int* perm, int top, 
             ATX_MOE_LAUNCH((moe_gemm_fma_kernel<float, false>), float);
     }
 #undef ATX_MOE_LAUNCH
+    return ATX_OK;
+}
+
+int atx_moe_gather_rows(const void* x, long long ldx, const int* perm, int top, const int* seg_off, int E, void* out,
+                        long long ldo, int max_slots, int W, int dtype, int flags, atx_stream_t stream) {
+    ATX_REQUIRE(x && perm && seg_off && out, "atx_moe_gather_rows: null pointer");
+    ATX_REQUIRE(max_slots > 0 && W > 0 && top > 0 && E > 0 && ldx >= W && ldo >= W, "atx_moe_gather_rows: bad shape slots=%d W=%d",
+                max_slots, W);
+    cudaLaunchConfig_t cfg = {};
+    cudaLaunchAttribute attr[1];
+    cfg.gridDim = dim3(max_slots);
+    cfg.blockDim = dim3(128);
+    cfg.stream = reinterpret_cast<cudaStream_t>(stream);
+    set_pdl_moe(cfg, attr, flags);
+    if (dtype == ATX_DT_F32)
+        ATX_CUDA(cudaLaunchKernelEx(&cfg, moe_gather_rows_kernel<float>, reinterpret_cast<const float*>(x), ldx, perm, top,
+                                    seg_off, E, reinterpret_cast<float*>(out), ldo, W));
+    else
+        ATX_CUDA(cudaLaunchKernelEx(&cfg, moe_gather_rows_kernel<__nv_bfloat16>, reinterpret_cast<const __nv_bfloat16*>(x), ldx,
+                                    perm, top, seg_off, E, reinterpret_cast<__nv_bfloat16*>(out), ldo, W));
     return ATX_OK;
 }
 

@@ -70,6 +70,13 @@ void atx_gemm_plan_destroy(atx_gemm_plan* plan);
 int atx_gemm_run(const atx_gemm_plan* plan, void* out, long long ldo, int T, int mode, int splits,
                  int flags, atx_stream_t stream);
 int atx_gemm_auto_splits(long long N, long long K, int T);
+/* The prefill-sized kernel over groups of rows that each have their own block of W (a mixture of experts: W stacks the
+ * experts' matrices, n_group rows each; X holds every expert's rows back to back). tiles / seg_off as atx_moe_plan writes
+ * them with tile_rows = atx_gemm_grouped_tile_rows(): out[slot, :] = X[slot, :] W_e^T for the slots of expert e. The grid
+ * is sized for max_row_tiles; the real count is read on the device. Modes that store (no ADD). */
+int atx_gemm_grouped_tile_rows(void);
+int atx_gemm_run_grouped(const atx_gemm_plan* plan, void* out, long long ldo, int n_group, int mode, const int* seg_off,
+                         const int* tiles, int max_row_tiles, int flags, atx_stream_t stream);
 
 /* ---- embedding gather: out[t, :] = float(table[ids[t], :]) ---------------------------------------
  * Replaces LlamaModel.embed_tokens (modeling_llama.py:375-427). table: [V, H] bf16, out fp32. */
@@ -455,11 +462,16 @@ int atx_moe_route(const float* logits, long long ld, const float* correction, in
                   float* wgt, int T, int flags, atx_stream_t stream);
 /* Sorts the n_pairs = T * top (token, choice) pairs by expert. Choices >= E (or < 0) take no slot. seg_off [E + 1]: first
  * slot of every expert; perm [n_pairs]: pair of a slot; slot_of [n_pairs]: slot of a pair (-1: none); tiles
- * [2 + 2 * max_tiles] int32: the tile count, a spare word, then (expert, first slot) per tile of atx_moe_tile_rows() slots;
- * max_tiles = ceil(n_pairs / tile rows) + E always suffices. */
+ * [2 + 2 * max_tiles] int32: the tile count, a spare word, then (expert, first slot) per tile of tile_rows slots
+ * (atx_moe_tile_rows() for atx_moe_expert_gemm, atx_gemm_grouped_tile_rows() for atx_gemm_run_grouped);
+ * max_tiles = ceil(n_pairs / tile_rows) + E always suffices. */
 int atx_moe_tile_rows(void);
-int atx_moe_plan(const int* sel, int n_pairs, int E, int* seg_off, int* perm, int* slot_of, int* tiles, int flags,
-                 atx_stream_t stream);
+int atx_moe_plan(const int* sel, int n_pairs, int E, int tile_rows, int* seg_off, int* perm, int* slot_of, int* tiles,
+                 int flags, atx_stream_t stream);
+/* out[slot, :] = x[perm[slot] / top, :] for the slots the plan handed out (at most max_slots): every expert's rows back to
+ * back, for atx_gemm_run_grouped. */
+int atx_moe_gather_rows(const void* x, long long ldx, const int* perm, int top, const int* seg_off, int E, void* out,
+                        long long ldo, int max_slots, int W, int dtype, int flags, atx_stream_t stream);
 /* out[slot, n] = sum_k A[row(slot), k] * W[e * expert_stride + n * ldw + k] for the slots of every expert e; row(slot) =
  * perm[slot] / top with gather != 0, else slot. gated == 0: fp32 out. gated != 0: W holds N gate rows then N up rows per
  * expert (interleaved != 0: blocks of 64 gate rows and 64 up rows in turn, the layout ATX_GEMM_SWIGLU_BF16 reads) and

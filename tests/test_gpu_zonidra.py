@@ -702,7 +702,7 @@ def test_polynomial_norm_activation_and_scaled_residual_norm(F):
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("E,ident,top,Fe,W,T", [(5, 2, 3, 24, 64, 150), (1, 0, 1, 8, 40, 7), (40, 3, 6, 16, 72, 130),
-                                               (3, 4, 7, 64, 128, 65), (6, 0, 2, 128, 192, 300)])
+                                               (3, 4, 7, 64, 128, 65), (6, 0, 2, 128, 192, 300), (9, 1, 2, 64, 64, 700)])
 def test_expert_mixture_kernels_route_sort_multiply_and_sum(E, ident, top, Fe, W, T, dtype):
     """Router logits built so that the choice differs from the plain arg-max (the correction decides) and the weight is
     the uncorrected score; every expert's rows go through its own matrices; identity choices return the input."""
@@ -737,7 +737,7 @@ def test_expert_mixture_kernels_route_sort_multiply_and_sum(E, ident, top, Fe, W
     max_tiles = (T * top + tr - 1) // tr + E
     seg, perm, slot_of = (torch.zeros(n, dtype=i32, device=DEV) for n in (E + 1, T * top, T * top))
     tiles = torch.zeros(2 + 2 * max_tiles, dtype=i32, device=DEV)
-    ck(L.atx_moe_plan(sel.data_ptr(), T * top, E, seg.data_ptr(), perm.data_ptr(), slot_of.data_ptr(), tiles.data_ptr(), 0, stream()))
+    ck(L.atx_moe_plan(sel.data_ptr(), T * top, E, tr, seg.data_ptr(), perm.data_ptr(), slot_of.data_ptr(), tiles.data_ptr(), 0, stream()))
     inter = 1 if (dtype == "bfloat16" and Fe % 64 == 0) else 0      # gate / up rows in blocks of 64, or gate rows then up rows
     if inter:
         w_gu = dev(torch.stack([torch.stack((wt[f"e{e}.gate"].view(Fe // 64, 64, W), wt[f"e{e}.up"].view(Fe // 64, 64, W)), 1)
@@ -760,3 +760,26 @@ def test_expert_mixture_kernels_route_sort_multiply_and_sum(E, ident, top, Fe, W
     assert seg.cpu().tolist() == [0] + counts.cumsum(0).tolist()
     err = float((y.double().cpu() - want).abs().max()) / float(want.abs().max())
     assert err < (1e-5 if dtype == "float32" else 0.03), err
+    if not inter:
+        return
+    # the same products on the tcgen05 GEMM: every expert's rows gathered back to back, tiles of its own row count
+    big = int(L.atx_gemm_grouped_tile_rows())
+    max_big = (T * top + big - 1) // big + E
+    tiles_b = torch.zeros(2 + 2 * max_big, dtype=i32, device=DEV)
+    ck(L.atx_moe_plan(sel.data_ptr(), T * top, E, big, seg.data_ptr(), perm.data_ptr(), slot_of.data_ptr(), tiles_b.data_ptr(), 0,
+                      stream()))
+    xperm = torch.zeros(T * top, W, dtype=xt, device=DEV)
+    ck(L.atx_moe_gather_rows(ud.data_ptr(), W, perm.data_ptr(), top, seg.data_ptr(), E, xperm.data_ptr(), W, T * top, W, dt, 0,
+                             stream()))
+    eact2, ye2 = torch.zeros(T * top, Fe, dtype=xt, device=DEV), torch.zeros(T * top, W, device=DEV)
+    p_gu, p_dn = C.GemmPlan(w_gu.view(E * 2 * Fe, W), xperm), C.GemmPlan(w_dn.view(E * W, Fe), eact2)
+    ck(L.atx_gemm_run_grouped(p_gu._h, eact2.data_ptr(), Fe, 2 * Fe, C.GEMM_SWIGLU_BF16, seg.data_ptr(), tiles_b.data_ptr(),
+                              max_big, 0, stream()))
+    ck(L.atx_gemm_run_grouped(p_dn._h, ye2.data_ptr(), W, W, C.GEMM_STORE_F32, seg.data_ptr(), tiles_b.data_ptr(), max_big, 0,
+                              stream()))
+    y2 = dev(ysh)
+    ck(L.atx_moe_combine(y2.data_ptr(), ye2.data_ptr(), W, ud.data_ptr(), sel.data_ptr(), wg.data_ptr(), slot_of.data_ptr(),
+                         ld.data_ptr() + 4 * Rn, Rn + 1, T, W, top, E, dt, 0, stream()))
+    torch.cuda.synchronize()
+    err = float((y2.double().cpu() - want).abs().max()) / float(want.abs().max())
+    assert err < 0.03, ("grouped", err)
