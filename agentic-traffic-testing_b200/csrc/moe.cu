@@ -194,6 +194,7 @@ moe_gemm_tc_kernel(const __nv_bfloat16* __restrict__ A, long long lda, const int
     const bool vec = (K & 7) == 0 && ((lda | ldw | expert_stride) & 7) == 0 &&
                      ((reinterpret_cast<unsigned long long>(A) | reinterpret_cast<unsigned long long>(W)) & 15) == 0;
     const int nk = (K + kEK - 1) / kEK;
+    const int rb = warp;   // a warp owns 16 rows and all 64 outputs of the tile
     auto load = [&](int kc, int stage) {
         __nv_bfloat16* sa = stages + stage * kStageElems;
         __nv_bfloat16* sw = sa + kET * kELD;
@@ -230,11 +231,11 @@ moe_gemm_tc_kernel(const __nv_bfloat16* __restrict__ A, long long lda, const int
         else asm volatile("cp.async.commit_group;" ::: "memory");
         const __nv_bfloat16* sa = stages + (kc % kEStages) * kStageElems;
         const __nv_bfloat16* sw = sa + kET * kELD;
-        if (warp * 16 < rows) {
+        if (rb * 16 < rows) {
 #pragma unroll
             for (int ks = 0; ks < kEK / 16; ++ks) {
                 uint32_t a[4];
-                ldsm_x4(smem_u32(sa + (warp * 16 + (lane & 15)) * kELD + ks * 16 + (lane >> 4) * 8), a[0], a[1], a[2], a[3]);
+                ldsm_x4(smem_u32(sa + (rb * 16 + (lane & 15)) * kELD + ks * 16 + (lane >> 4) * 8), a[0], a[1], a[2], a[3]);
 #pragma unroll
                 for (int g = 0; g < NW; ++g) {
 #pragma unroll
@@ -252,7 +253,7 @@ moe_gemm_tc_kernel(const __nv_bfloat16* __restrict__ A, long long lda, const int
     asm volatile("cp.async.wait_group 0;" ::: "memory");
 #pragma unroll
     for (int rr = 0; rr < 2; ++rr) {
-        const int r = warp * 16 + (lane >> 2) + 8 * rr;
+        const int r = rb * 16 + (lane >> 2) + 8 * rr;
         if (r >= rows) continue;
         const long long p = p0 + r;
 #pragma unroll
@@ -377,19 +378,52 @@ __global__ void __launch_bounds__(256)
 moe_combine_kernel(float* __restrict__ y, const float* __restrict__ ye, long long lde, const XT* __restrict__ x,
                    const int* __restrict__ sel, const float* __restrict__ wgt, const int* __restrict__ slot_of,
                    const float* __restrict__ shared_gate, long long ldsg, int W, int top, int E) {
+    __shared__ float s_w[64];
+    __shared__ long long s_row[64];   // row of ye, or -1: the choice returns the input
     pdl_launch_dependents();
     pdl_wait();
     const long long t = blockIdx.x;
+    for (int k = threadIdx.x; k < top; k += blockDim.x) {
+        s_w[k] = wgt[t * top + k];
+        s_row[k] = sel[t * top + k] >= E ? -1 : static_cast<long long>(slot_of[t * top + k]) * lde;
+    }
     const float sg = shared_gate ? 1.f / (1.f + expf(-shared_gate[t * ldsg])) : 0.f;
-    for (int i = threadIdx.x; i < W; i += blockDim.x) {
-        float acc = shared_gate ? sg * y[t * W + i] : 0.f;
-        for (int k = 0; k < top; ++k) {
-            const int e = sel[t * top + k];
-            const float w = wgt[t * top + k];
-            const float v = e >= E ? mld(x, t * W + i) : ye[static_cast<long long>(slot_of[t * top + k]) * lde + i];
-            acc = fmaf(w, v, acc);
+    __syncthreads();
+    float* yr = y + t * W;
+    const XT* xr = x + t * W;
+    if ((W & 3) == 0 && (lde & 3) == 0 &&
+        ((reinterpret_cast<unsigned long long>(y) | reinterpret_cast<unsigned long long>(ye) |
+          reinterpret_cast<unsigned long long>(x)) & 15) == 0) {
+        for (int i = threadIdx.x; i < W / 4; i += blockDim.x) {
+            float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (shared_gate) {
+                const float4 v = reinterpret_cast<const float4*>(yr)[i];
+                acc = make_float4(sg * v.x, sg * v.y, sg * v.z, sg * v.w);
+            }
+            float4 xin = make_float4(0.f, 0.f, 0.f, 0.f);
+            bool have_x = false;
+            for (int k = 0; k < top; ++k) {
+                float4 v;
+                if (s_row[k] < 0) {
+                    if (!have_x) {
+                        xin = make_float4(mld(xr, 4 * i), mld(xr, 4 * i + 1), mld(xr, 4 * i + 2), mld(xr, 4 * i + 3));
+                        have_x = true;
+                    }
+                    v = xin;
+                } else {
+                    v = *reinterpret_cast<const float4*>(ye + s_row[k] + 4 * i);
+                }
+                const float w = s_w[k];
+                acc.x = fmaf(w, v.x, acc.x), acc.y = fmaf(w, v.y, acc.y), acc.z = fmaf(w, v.z, acc.z), acc.w = fmaf(w, v.w, acc.w);
+            }
+            reinterpret_cast<float4*>(yr)[i] = acc;
         }
-        y[t * W + i] = acc;
+        return;
+    }
+    for (int i = threadIdx.x; i < W; i += blockDim.x) {
+        float acc = shared_gate ? sg * yr[i] : 0.f;
+        for (int k = 0; k < top; ++k) acc = fmaf(s_w[k], s_row[k] < 0 ? mld(xr, i) : ye[s_row[k] + i], acc);
+        yr[i] = acc;
     }
 }
 
@@ -500,7 +534,8 @@ int atx_moe_combine(float* y, const float* ye, long long lde, const void* x, con
                     const int* slot_of, const float* shared_gate, long long ldsg, int T, int W, int top, int E, int dtype,
                     int flags, atx_stream_t stream) {
     ATX_REQUIRE(y && ye && x && sel && wgt && slot_of, "atx_moe_combine: null pointer");
-    ATX_REQUIRE(T > 0 && W > 0 && top > 0 && E > 0 && lde >= W, "atx_moe_combine: bad shape T=%d W=%d top=%d", T, W, top);
+    ATX_REQUIRE(T > 0 && W > 0 && top > 0 && top <= 64 && E > 0 && lde >= W, "atx_moe_combine: bad shape T=%d W=%d top=%d (<= 64)",
+                T, W, top);
     cudaLaunchConfig_t cfg = {};
     cudaLaunchAttribute attr[1];
     cfg.gridDim = dim3(T);
