@@ -257,8 +257,8 @@ def test_mixed_batches_equal_each_request_alone(dtype):
 def test_bf16_portions_on_the_tensor_cores_beside_single_tokens():
     """Sizes with a tensor-core attention kernel: portions (prompt form) beside single tokens (decode form, several key
     slices) in one step, kept keys and the window's edge inside and outside of tiles."""
-    cfg = model_cfg([layer(heads=4, kv=2, dim=64, vdim=32, size=70, keep=20, rot_dims=16, scale=0.125, mlp=dense(128)),
-                     layer(heads=8, kv=2, dim=64, vdim=32, size=100, keep=3, rot_dims=16, scale=0.125, kv_from=0,
+    cfg = model_cfg([layer(heads=4, kv=2, dim=64, vdim=48, size=70, keep=18, rot_dims=24, scale=0.125, mlp=dense(128)),
+                     layer(heads=6, kv=2, dim=64, vdim=48, size=100, keep=3, rot_dims=24, scale=0.125, kv_from=0,
                            mlp=moe(4, 2, 2, 64, 64))], width=128)
     wt = R.random_checkpoint(cfg, 10)
     reqs = {"a": tokens(230, seed=1), "b": tokens(150, seed=2), "c": tokens(200, seed=3)}
@@ -392,8 +392,8 @@ def test_greedy_generation_matches_the_reference(mode):
 def test_bf16_greedy_generation_on_the_tensor_core_kernels(mode):
     from atx.scheduler import SamplingParams
 
-    cfg = model_cfg([layer(heads=4, kv=2, dim=64, vdim=32, size=40, keep=6, rot_dims=32, scale=0.125, mlp=dense(128)),
-                     layer(heads=8, kv=2, dim=64, vdim=32, size=90, keep=0, rot_dims=32, scale=0.125, kv_from=0,
+    cfg = model_cfg([layer(heads=4, kv=2, dim=64, vdim=40, size=40, keep=6, rot_dims=32, scale=0.125, mlp=dense(128)),
+                     layer(heads=6, kv=2, dim=64, vdim=40, size=90, keep=0, rot_dims=32, scale=0.125, kv_from=0,
                            mlp=moe(6, 2, 2, 64, 128)),
                      layer(heads=6, kv=2, dim=24, vdim=32, size=70, keep=12, rot_dims=24, scale=0.2)], width=128)
     wt = R.random_checkpoint(cfg, 17)
@@ -521,8 +521,8 @@ def test_row_attention_window_edges_kept_keys_bias_and_gate(window, keep, n, dty
     assert err < (1e-4 if dtype == "float32" else 0.05), (window, keep, n, err)
 
 
-@pytest.mark.parametrize("D,Vd,window,keep,pos0,n", [(64, 64, 70, 5, 0, 200), (64, 32, 64, 64, 0, 193), (128, 128, 100, 20, 37, 150),
-                                                      (72, 40, 33, 66, 0, 130), (64, 64, 3, 130, 5, 190), (64, 32, 136, 20, 100, 90)])
+@pytest.mark.parametrize("D,Vd,window,keep,pos0,n", [(64, 64, 70, 5, 0, 200), (64, 24, 64, 64, 0, 193), (128, 128, 100, 20, 37, 150),
+                                                      (72, 40, 33, 66, 0, 130), (64, 64, 3, 130, 5, 190), (64, 48, 150, 24, 100, 90)])
 def test_tensor_core_attention_window_edges_and_kept_keys(D, Vd, window, keep, pos0, n):
     """The prompt form over a portion that starts at pos0 (earlier keys already in the pages), and the decode form for the
     same rows one by one with 1, 3 and 7 key slices."""
