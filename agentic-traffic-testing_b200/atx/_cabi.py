@@ -190,7 +190,7 @@ def load() -> C.CDLL:
     lib.atx_moe_gather_rows.argtypes = [vp, i64, vp, i32, vp, i32, vp, i64, i32, i32, i32, i32, vp]
     lib.atx_gemm_run_grouped.argtypes = [vp, vp, i64, i32, i32, vp, vp, i32, i32, vp]
     lib.atx_gemm_grouped_tile_rows.argtypes = []
-    lib.atx_moe_expert_gemm.argtypes = [vp, i64, vp, i32, i32, vp, i64, i64, vp, i64, i32, i32, i32, i32, vp, vp, i32, i32, i32, vp]
+    lib.atx_moe_expert_gemm.argtypes = [vp, i64, vp, i32, i32, vp, i64, i64, vp, i64, i32, i32, i32, i32, i32, vp, vp, i32, i32, i32, vp]
     lib.atx_moe_combine.argtypes = [vp, vp, i64, vp, vp, vp, vp, vp, i64, i32, i32, i32, i32, i32, i32, vp]
     for name in EXPORTS:  # fail at load time, not at first use, if the build is stale
         getattr(lib, name)

@@ -426,7 +426,8 @@ class Program:
         # mixture of experts: choices, weights, the plan, the experts' hidden rows and outputs per (token, choice) slot
         self.tile_rows = int(lib.atx_moe_tile_rows())
         P = T * n_pairs
-        self.max_tiles = (P + self.tile_rows - 1) // self.tile_rows + n_exp
+        # tiles of 64 slots, or of 16 for decode-sized steps (at most 64 tokens): whichever list is longer
+        self.max_tiles = max((P + self.tile_rows - 1) // self.tile_rows, (min(P, 64 * n_pairs) + 15) // 16) + n_exp
         self.sel = torch.zeros(P, dtype=i32, device=dev)
         self.wgt = torch.zeros(P, dtype=f32, device=dev)
         self.seg_off = torch.zeros(n_exp + 1, dtype=i32, device=dev)
@@ -658,12 +659,14 @@ class Program:
                                                 st))
                     n += 1
                 else:
-                    tiles, tl = min(self.max_tiles, (pairs + self.tile_rows - 1) // self.tile_rows + E), self.tiles.data_ptr()
-                    ck(lib.atx_moe_plan(self.sel.data_ptr(), pairs, E, self.tile_rows, so, pm, sl, tl, fl, st))
+                    # decode-sized bf16 steps: tiles of 16 slots (one or two rows per expert), more CTAs per SM
+                    tr = 16 if (small and dt == _cabi.DT_BF16) else self.tile_rows
+                    tiles, tl = min(self.max_tiles, (pairs + tr - 1) // tr + E), self.tiles.data_ptr()
+                    ck(lib.atx_moe_plan(self.sel.data_ptr(), pairs, E, tr, so, pm, sl, tl, fl, st))
                     ck(lib.atx_moe_expert_gemm(xn, W, pm, top, 1, l.w_egu.data_ptr(), 2 * Fe * W, W, self.eact.data_ptr(), Fe, Fe,
-                                               W, 1, 1 if l.egu_interleaved else 0, so, tl, tiles, dt, fl, st))
+                                               W, 1, 1 if l.egu_interleaved else 0, tr, so, tl, tiles, dt, fl, st))
                     ck(lib.atx_moe_expert_gemm(self.eact.data_ptr(), Fe, None, top, 0, l.w_edown.data_ptr(), W * Fe, Fe,
-                                               self.ye.data_ptr(), W, W, Fe, 0, 0, so, tl, tiles, dt, fl, st))
+                                               self.ye.data_ptr(), W, W, Fe, 0, 0, tr, so, tl, tiles, dt, fl, st))
                 n += 5
                 if shared:
                     if l.sgu_interleaved:

@@ -160,28 +160,30 @@ __device__ __forceinline__ void moe_cp16(void* smem_dst, const void* gsrc, bool 
 // 128 (n / 64) + n % 64 and 64 further (the layout of the tcgen05 GEMM's gated epilogue). Tiles of 64 reduction
 // elements arrive by cp.async into three stages, two in flight while one is multiplied: with one or two rows per expert
 // (decoded tokens) the kernel only streams the chosen experts' matrices, and what bounds it is bytes in flight.
-template <bool GATED>
+// BM: slots per tile, 64 or 16. Decode-sized steps have one or two rows per expert; with 16-slot tiles a stage holds a third
+// less, three CTAs instead of two fit an SM, and the grid (tiles x output blocks) fits one wave.
+template <bool GATED, int BM>
 __global__ void __launch_bounds__(128)
 moe_gemm_tc_kernel(const __nv_bfloat16* __restrict__ A, long long lda, const int* __restrict__ perm, int top, int gather,
                    const __nv_bfloat16* __restrict__ W, long long expert_stride, long long ldw, void* __restrict__ out,
                    long long ldo, int N, int K, const int* __restrict__ seg_off, const int* __restrict__ tiles,
                    int interleaved) {
     constexpr int NW = GATED ? 2 : 1;
-    constexpr int kStageElems = (1 + NW) * kET * kELD;
+    constexpr int kStageElems = (BM + NW * kET) * kELD;
     extern __shared__ __align__(16) unsigned char moe_smem[];
     __nv_bfloat16* stages = reinterpret_cast<__nv_bfloat16*>(moe_smem);
-    __shared__ long long arow[kET];
+    __shared__ long long arow[BM];
     pdl_launch_dependents();
     pdl_wait();
     if (static_cast<int>(blockIdx.y) >= tiles[0]) return;
     const int e = tiles[2 + 2 * blockIdx.y], p0 = tiles[3 + 2 * blockIdx.y];
-    const int rows = min(kET, seg_off[e + 1] - p0);
+    const int rows = min(BM, seg_off[e + 1] - p0);
     const int n0 = blockIdx.x * kET;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const __nv_bfloat16* We = W + static_cast<long long>(e) * expert_stride;
     const long long g_base = (GATED && interleaved) ? 2ll * n0 : n0;          // matrix row of the tile's first gate output
     const long long u_base = (GATED && interleaved) ? 2ll * n0 + 64 : static_cast<long long>(N) + n0;
-    if (threadIdx.x < kET) {
+    if (threadIdx.x < BM) {
         const int p = p0 + threadIdx.x;
         arow[threadIdx.x] = threadIdx.x < rows ? static_cast<long long>(gather ? perm[p] / top : p) * lda : -1;
     }
@@ -197,14 +199,17 @@ moe_gemm_tc_kernel(const __nv_bfloat16* __restrict__ A, long long lda, const int
     const int rb = warp;   // a warp owns 16 rows and all 64 outputs of the tile
     auto load = [&](int kc, int stage) {
         __nv_bfloat16* sa = stages + stage * kStageElems;
-        __nv_bfloat16* sw = sa + kET * kELD;
+        __nv_bfloat16* sw = sa + BM * kELD;
         const int k0 = kc * kEK;
         if (vec) {
             for (int c = threadIdx.x; c < kET * (kEK / 8); c += 128) {
                 const int r = c / (kEK / 8), k8 = (c - r * (kEK / 8)) * 8;
                 const int k = k0 + k8, n = n0 + r;
-                const bool a_ok = arow[r] >= 0 && k < K, w_ok = n < N && k < K;
-                moe_cp16(sa + r * kELD + k8, A + (a_ok ? arow[r] + k : 0), a_ok);
+                const bool w_ok = n < N && k < K;
+                if (r < BM) {
+                    const bool a_ok = arow[r] >= 0 && k < K;
+                    moe_cp16(sa + r * kELD + k8, A + (a_ok ? arow[r] + k : 0), a_ok);
+                }
                 moe_cp16(sw + r * kELD + k8, We + (w_ok ? (g_base + r) * ldw + k : 0), w_ok);
                 if (GATED) moe_cp16(sw + (kET + r) * kELD + k8, We + (w_ok ? (u_base + r) * ldw + k : 0), w_ok);
             }
@@ -213,7 +218,7 @@ moe_gemm_tc_kernel(const __nv_bfloat16* __restrict__ A, long long lda, const int
             for (int c = threadIdx.x; c < kET * kEK; c += 128) {
                 const int r = c / kEK, kk = c - r * kEK;
                 const int k = k0 + kk, n = n0 + r;
-                sa[r * kELD + kk] = (arow[r] >= 0 && k < K) ? A[arow[r] + k] : zero;
+                if (r < BM) sa[r * kELD + kk] = (arow[r] >= 0 && k < K) ? A[arow[r] + k] : zero;
                 sw[r * kELD + kk] = (n < N && k < K) ? We[(g_base + r) * ldw + k] : zero;
                 if (GATED) sw[(kET + r) * kELD + kk] = (n < N && k < K) ? We[(u_base + r) * ldw + k] : zero;
             }
@@ -230,7 +235,7 @@ moe_gemm_tc_kernel(const __nv_bfloat16* __restrict__ A, long long lda, const int
         if (kc + kEStages - 1 < nk) load(kc + kEStages - 1, (kc + kEStages - 1) % kEStages);
         else asm volatile("cp.async.commit_group;" ::: "memory");
         const __nv_bfloat16* sa = stages + (kc % kEStages) * kStageElems;
-        const __nv_bfloat16* sw = sa + kET * kELD;
+        const __nv_bfloat16* sw = sa + BM * kELD;
         if (rb * 16 < rows) {
 #pragma unroll
             for (int ks = 0; ks < kEK / 16; ++ks) {
@@ -468,12 +473,14 @@ int atx_moe_plan(const int* sel, int n_pairs, int E, int tile_rows, int* seg_off
 
 int atx_moe_expert_gemm(const void* A, long long lda, const int* perm, int top, int gather, const void* W,
                         long long expert_stride, long long ldw, void* out, long long ldo, int N, int K, int gated,
-                        int interleaved, const int* seg_off, const int* tiles, int max_tiles, int dtype, int flags,
-                        atx_stream_t stream) {
+                        int interleaved, int tile_rows, const int* seg_off, const int* tiles, int max_tiles, int dtype,
+                        int flags, atx_stream_t stream) {
     ATX_REQUIRE(A && W && out && seg_off && tiles && (!gather || perm), "atx_moe_expert_gemm: null pointer");
     ATX_REQUIRE(N > 0 && K > 0 && max_tiles > 0 && max_tiles <= 65535 && top > 0 && ldw >= K && lda >= K && ldo >= N,
                 "atx_moe_expert_gemm: bad shape N=%d K=%d tiles=%d lda=%lld ldw=%lld ldo=%lld", N, K, max_tiles, lda, ldw, ldo);
     ATX_REQUIRE(!interleaved || (gated && N % 64 == 0), "atx_moe_expert_gemm: interleaved gate / up rows need N %% 64 == 0");
+    ATX_REQUIRE(tile_rows == kET || (tile_rows == 16 && dtype == ATX_DT_BF16),
+                "atx_moe_expert_gemm: tiles of %d slots (64, or 16 for bf16)", tile_rows);
     cudaLaunchConfig_t cfg = {};
     cudaLaunchAttribute attr[1];
     cfg.gridDim = dim3((N + kET - 1) / kET, max_tiles);
@@ -485,20 +492,23 @@ int atx_moe_expert_gemm(const void* A, long long lda, const int* perm, int top, 
                                 interleaved))
     if (dtype == ATX_DT_BF16) {
         cfg.blockDim = dim3(128);
-        const int smem = kEStages * ((gated ? 3 : 2) * kET * kELD) * 2;
+        const int smem = kEStages * ((tile_rows + (gated ? 2 : 1) * kET) * kELD) * 2;
         cfg.dynamicSmemBytes = smem;
-        static bool attr_done[2] = {false, false};
-        if (!attr_done[gated ? 1 : 0]) {
-            if (gated)
-                ATX_CUDA(cudaFuncSetAttribute(moe_gemm_tc_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
-            else
-                ATX_CUDA(cudaFuncSetAttribute(moe_gemm_tc_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
-            attr_done[gated ? 1 : 0] = true;
-        }
-        if (gated)
-            ATX_MOE_LAUNCH(moe_gemm_tc_kernel<true>, __nv_bfloat16);
-        else
-            ATX_MOE_LAUNCH(moe_gemm_tc_kernel<false>, __nv_bfloat16);
+        static bool attr_done[4] = {false, false, false, false};
+        const int which = (gated ? 1 : 0) + (tile_rows == 16 ? 2 : 0);
+#define ATX_MOE_TC(G_, BM_)                                                                                              \
+    do {                                                                                                                 \
+        if (!attr_done[which]) {                                                                                         \
+            ATX_CUDA(cudaFuncSetAttribute(moe_gemm_tc_kernel<G_, BM_>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem)); \
+            attr_done[which] = true;                                                                                     \
+        }                                                                                                                \
+        ATX_MOE_LAUNCH((moe_gemm_tc_kernel<G_, BM_>), __nv_bfloat16);                                                    \
+    } while (0)
+        if (gated && tile_rows == 16) ATX_MOE_TC(true, 16);
+        else if (gated) ATX_MOE_TC(true, 64);
+        else if (tile_rows == 16) ATX_MOE_TC(false, 16);
+        else ATX_MOE_TC(false, 64);
+#undef ATX_MOE_TC
     } else {
         cfg.blockDim = dim3(256);
         if (gated)

@@ -475,12 +475,13 @@ int atx_moe_gather_rows(const void* x, long long ldx, const int* perm, int top, 
 /* out[slot, n] = sum_k A[row(slot), k] * W[e * expert_stride + n * ldw + k] for the slots of every expert e; row(slot) =
  * perm[slot] / top with gather != 0, else slot. gated == 0: fp32 out. gated != 0: W holds N gate rows then N up rows per
  * expert (interleaved != 0: blocks of 64 gate rows and 64 up rows in turn, the layout ATX_GEMM_SWIGLU_BF16 reads) and
- * out (element type) = silu(gate) * up. bf16 on the tensor cores, fp32 on the FMA pipe. The grid covers max_tiles tiles;
- * CTAs beyond the plan's count return. */
+ * out (element type) = silu(gate) * up. bf16 on the tensor cores, fp32 on the FMA pipe. tile_rows: the slots per tile the
+ * plan was made with, atx_moe_tile_rows(), or 16 (bf16 only: decode-sized steps, more CTAs per SM). The grid covers
+ * max_tiles tiles; CTAs beyond the plan's count return. */
 int atx_moe_expert_gemm(const void* A, long long lda, const int* perm, int top, int gather, const void* W,
                         long long expert_stride, long long ldw, void* out, long long ldo, int N, int K, int gated,
-                        int interleaved, const int* seg_off, const int* tiles, int max_tiles, int dtype, int flags,
-                        atx_stream_t stream);
+                        int interleaved, int tile_rows, const int* seg_off, const int* tiles, int max_tiles, int dtype,
+                        int flags, atx_stream_t stream);
 /* y[t, :] = sigmoid(shared_gate[t * ldsg]) * y[t, :] (shared_gate nullable: y is overwritten) + sum_k wgt[t, k] *
  * (sel[t, k] >= E ? x[t, :] : ye[slot_of[t * top + k], :]). y, ye fp32; x of the element type. */
 int atx_moe_combine(float* y, const float* ye, long long lde, const void* x, const int* sel, const float* wgt,
