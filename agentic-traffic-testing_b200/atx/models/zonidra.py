@@ -659,8 +659,10 @@ class Program:
                                                 st))
                     n += 1
                 else:
-                    # decode-sized bf16 steps: tiles of 16 slots (one or two rows per expert), more CTAs per SM
-                    tr = 16 if (small and dt == _cabi.DT_BF16) else self.tile_rows
+                    # decode-sized bf16 steps (one or two rows per expert): tiles of 16 slots put three CTAs on an SM instead
+                    # of two. That pays when two per SM would need a second wave, and costs a little when one wave suffices.
+                    ctas = min(E, pairs) * ((Fe + 63) // 64)
+                    tr = 16 if (small and dt == _cabi.DT_BF16 and ctas > 2 * self.sms) else self.tile_rows
                     tiles, tl = min(self.max_tiles, (pairs + tr - 1) // tr + E), self.tiles.data_ptr()
                     ck(lib.atx_moe_plan(self.sel.data_ptr(), pairs, E, tr, so, pm, sl, tl, fl, st))
                     ck(lib.atx_moe_expert_gemm(xn, W, pm, top, 1, l.w_egu.data_ptr(), 2 * Fe * W, W, self.eact.data_ptr(), Fe, Fe,
