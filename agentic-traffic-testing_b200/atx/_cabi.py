@@ -46,6 +46,8 @@ EXPORTS = [
     "atx_attn_paged", "atx_attn_paged_prefill", "atx_attn_paged_decode",
     "atx_moe_route", "atx_moe_tile_rows", "atx_moe_plan", "atx_moe_expert_gemm", "atx_moe_combine", "atx_moe_gather_rows",
     "atx_gemm_run_grouped", "atx_gemm_grouped_tile_rows",
+    "atx_resid_norm_out", "atx_gated_act_clamped", "atx_gated_norm_groups", "atx_conv_residual", "atx_lowrank_logdecay",
+    "atx_gated_linear_recurrence", "atx_moe_route_opts",
 ]
 ATTN_SOFTMAX = 0
 ATTN_SIGMOID = 1
@@ -192,6 +194,14 @@ def load() -> C.CDLL:
     lib.atx_gemm_grouped_tile_rows.argtypes = []
     lib.atx_moe_expert_gemm.argtypes = [vp, i64, vp, i32, i32, vp, i64, i64, vp, i64, i32, i32, i32, i32, i32, vp, vp, i32, i32, i32, vp]
     lib.atx_moe_combine.argtypes = [vp, vp, i64, vp, vp, vp, vp, vp, i64, i32, i32, i32, i32, i32, i32, vp]
+    lib.atx_resid_norm_out.argtypes = [vp, vp, vp, vp, vp, vp, vp, i32, f32, vp, i32, i32, f32, i32, vp, i64, i32, i32, vp]
+    lib.atx_gated_act_clamped.argtypes = [vp, vp, i32, i32, f32, f32, f32, i32, i32, vp]
+    lib.atx_gated_norm_groups.argtypes = [vp, i64, vp, i64, vp, i32, vp, i64, i32, i32, i32, f32, i32, f32, i32, i32, vp]
+    lib.atx_conv_residual.argtypes = [vp, i64, vp, vp, vp, i64, vp, vp, vp, vp, i32, i32, i32, i32, i32, vp]
+    lib.atx_lowrank_logdecay.argtypes = [vp, i64, vp, vp, vp, i64, i32, i32, i32, f32, i32, i32, vp]
+    lib.atx_gated_linear_recurrence.argtypes = [vp, i64, vp, i64, vp, i64, vp, i64, i32, i32, i32, f32, vp, vp, i64, vp, vp,
+                                                vp, vp, i32, i32, vp]
+    lib.atx_moe_route_opts.argtypes = [vp, i64, vp, i32, i32, f32, i32, vp, vp, i32, i32, vp]
     for name in EXPORTS:  # fail at load time, not at first use, if the build is stale
         getattr(lib, name)
     _lib = lib

@@ -10,9 +10,9 @@ from typing import Optional
 
 
 def _entries():
-    from . import gopopel, safisun, zonidra
+    from . import gopopel, napuzen, safisun, zonidra
 
-    return {"safisun": safisun, "gopopel": gopopel, "zonidra": zonidra}
+    return {"safisun": safisun, "gopopel": gopopel, "zonidra": zonidra, "napuzen": napuzen}
 
 
 def _module(arch: str):

@@ -76,3 +76,33 @@ def rotation_table_for(freqs: List[float], max_pos: int, device: torch.device) -
     """[max_pos, 2 * len(freqs)] fp32: cos then sin of p * f_i for the given frequencies, evaluated in float64 on the host."""
     ang = torch.arange(max_pos, dtype=torch.float64)[:, None] * torch.tensor(freqs, dtype=torch.float64)[None, :]
     return torch.cat((ang.cos(), ang.sin()), -1).to(torch.float32).contiguous().to(device)
+
+
+def stretched_frequencies(base: float, dims: int, scaling: Optional[dict]) -> "tuple[List[float], float]":
+    """f_i = base^(-2i/dims), i < dims/2, stretched by pair index (`scaling` = factor, original, fast, slow; None: as they
+    are), and the magnitude that multiplies every cosine and sine. A pair that makes t turns over `original` positions has
+    the index d(t) = dims ln(original / (2 pi t)) / (2 ln base); with lo = floor(d(fast)) and hi = ceil(d(slow)), clipped to
+    [0, dims - 1], the share s_i = clamp((i - lo) / max(hi - lo, 0.001), 0, 1) of f_i is divided by factor:
+    f_i (1 - s_i) + f_i s_i / factor. Magnitude 0.1 ln(factor) + 1. Float64 on the host."""
+    freqs = [float(base) ** (-2.0 * i / dims) for i in range(dims // 2)]
+    if not scaling:
+        return freqs, 1.0
+    factor, orig = float(scaling["factor"]), float(scaling["original"])
+
+    def index_of(turns: float) -> float:
+        return dims * math.log(orig / (2.0 * math.pi * turns)) / (2.0 * math.log(float(base)))
+
+    lo = max(math.floor(index_of(float(scaling["fast"]))), 0)
+    hi = min(math.ceil(index_of(float(scaling["slow"]))), dims - 1)
+    out = []
+    for i, f in enumerate(freqs):
+        s = min(max((i - lo) / max(hi - lo, 0.001), 0.0), 1.0)
+        out.append(f / factor * s + f * (1.0 - s))
+    return out, 0.1 * math.log(factor) + 1.0
+
+
+def rotation_table_scaled(freqs: List[float], magnitude: float, max_pos: int, device: torch.device) -> torch.Tensor:
+    """rotation_table_for with every cosine and sine multiplied by `magnitude` (the rotation kernels apply the table's
+    entries as they are, so a rotated pair comes out scaled)."""
+    ang = torch.arange(max_pos, dtype=torch.float64)[:, None] * torch.tensor(freqs, dtype=torch.float64)[None, :]
+    return (torch.cat((ang.cos(), ang.sin()), -1) * magnitude).to(torch.float32).contiguous().to(device)

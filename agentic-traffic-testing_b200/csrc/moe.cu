@@ -43,7 +43,7 @@ constexpr int kRouteMax = 16;   // router outputs per lane: up to 512 outputs
 
 __global__ void __launch_bounds__(128)
 moe_route_kernel(const float* __restrict__ logits, long long ld, const float* __restrict__ correction, int R, int top,
-                 float scale, int* __restrict__ sel, float* __restrict__ wgt, int T) {
+                 float scale, int* __restrict__ sel, float* __restrict__ wgt, int T, int normalize) {
     pdl_launch_dependents();
     pdl_wait();
     const int lane = threadIdx.x & 31;
@@ -74,6 +74,7 @@ moe_route_kernel(const float* __restrict__ logits, long long ld, const float* __
         s[i] *= inv;
         c[i] = e < R ? s[i] + (correction ? correction[e] : 0.f) : -INFINITY;
     }
+    float chosen = 0.f;   // sum of the chosen scores
     for (int k = 0; k < top; ++k) {
         float best = -INFINITY, bs = 0.f;
         int bi = 0x7fffffff;
@@ -92,10 +93,15 @@ moe_route_kernel(const float* __restrict__ logits, long long ld, const float* __
 #pragma unroll
         for (int i = 0; i < kRouteMax; ++i)
             if (lane + 32 * i == bi) c[i] = -INFINITY;
+        chosen += bs;
         if (lane == 0) {
             sel[t * top + k] = bi;
-            wgt[t * top + k] = bs * scale;
+            wgt[t * top + k] = normalize ? bs : bs * scale;
         }
+    }
+    if (normalize && lane == 0) {   // weights = chosen scores divided by their sum, times scale
+        const float inv_c = 1.f / (chosen + 1e-20f);
+        for (int k = 0; k < top; ++k) wgt[t * top + k] = wgt[t * top + k] * inv_c * scale;
     }
 }
 
@@ -440,6 +446,11 @@ extern "C" {
 
 int atx_moe_route(const float* logits, long long ld, const float* correction, int R, int top, float scale, int* sel,
                   float* wgt, int T, int flags, atx_stream_t stream) {
+    return atx_moe_route_opts(logits, ld, correction, R, top, scale, 0, sel, wgt, T, flags, stream);
+}
+
+int atx_moe_route_opts(const float* logits, long long ld, const float* correction, int R, int top, float scale,
+                       int normalize, int* sel, float* wgt, int T, int flags, atx_stream_t stream) {
     ATX_REQUIRE(logits && sel && wgt, "atx_moe_route: null pointer");
     ATX_REQUIRE(T > 0 && R > 0 && R <= 32 * kRouteMax && top > 0 && top <= R && ld >= R,
                 "atx_moe_route: bad shape T=%d outputs=%d (<= %d) top=%d ld=%lld", T, R, 32 * kRouteMax, top, ld);
@@ -449,7 +460,7 @@ int atx_moe_route(const float* logits, long long ld, const float* correction, in
     cfg.blockDim = dim3(128);
     cfg.stream = reinterpret_cast<cudaStream_t>(stream);
     set_pdl_moe(cfg, attr, flags);
-    ATX_CUDA(cudaLaunchKernelEx(&cfg, moe_route_kernel, logits, ld, correction, R, top, scale, sel, wgt, T));
+    ATX_CUDA(cudaLaunchKernelEx(&cfg, moe_route_kernel, logits, ld, correction, R, top, scale, sel, wgt, T, normalize));
     return ATX_OK;
 }
 

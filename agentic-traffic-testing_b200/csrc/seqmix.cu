@@ -127,7 +127,7 @@ __global__ void __launch_bounds__(1024)
 resid_norm_kernel(float* __restrict__ h, float* __restrict__ y, const XT* __restrict__ w_post,
                   const XT* __restrict__ post_scale, const XT* __restrict__ vec, const XT* __restrict__ w_pre,
                   OT* __restrict__ out, const int* __restrict__ rows, int T, int W, float eps, int zero_y,
-                  uint4* __restrict__ zero_ptr, long long zero_vecs) {
+                  uint4* __restrict__ zero_ptr, long long zero_vecs, float out_scale) {
     extern __shared__ __align__(16) float srow[];
     __shared__ float red[32];
     pdl_launch_dependents();
@@ -173,8 +173,12 @@ resid_norm_kernel(float* __restrict__ h, float* __restrict__ y, const XT* __rest
         }
         v.x += vc4.x, v.y += vc4.y, v.z += vc4.z, v.w += vc4.w;
         if (on && (y || vec) && !rows) st4(hr, i, v);
-        if (!w_pre) return;
-        const float rs = rsqrtf(block_sum(v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w, red) / static_cast<float>(W) + eps);
+        if (!out) return;
+        if (!w_pre) {   // no norm in front of the consumer: the row itself in the element type
+            if (on) st4(out + static_cast<long long>(t) * W, i, make_float4(v.x * out_scale, v.y * out_scale, v.z * out_scale, v.w * out_scale));
+            return;
+        }
+        const float rs = rsqrtf(block_sum(v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w, red) / static_cast<float>(W) + eps) * out_scale;
         if (on) st4(out + static_cast<long long>(t) * W, i, make_float4(v.x * rs * wq4.x, v.y * rs * wq4.y, v.z * rs * wq4.z, v.w * rs * wq4.w));
         return;
     }
@@ -211,9 +215,16 @@ resid_norm_kernel(float* __restrict__ h, float* __restrict__ y, const XT* __rest
             srow4[i] = v;
             ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
         }
-        if (!w_pre) return;
-        const float rs = rsqrtf(block_sum(ss, red) / static_cast<float>(W) + eps);
+        if (!out) return;
         OT* o = out + static_cast<long long>(t) * W;
+        if (!w_pre) {
+            for (int i = threadIdx.x; i < W4; i += blockDim.x) {   // each thread re-reads what it wrote itself
+                const float4 a = srow4[i];
+                st4(o, i, make_float4(a.x * out_scale, a.y * out_scale, a.z * out_scale, a.w * out_scale));
+            }
+            return;
+        }
+        const float rs = rsqrtf(block_sum(ss, red) / static_cast<float>(W) + eps) * out_scale;
         for (int i = threadIdx.x; i < W4; i += blockDim.x) {
             const float4 a = srow4[i], wq = ld4(w_pre, i);
             st4(o, i, make_float4(a.x * rs * wq.x, a.y * rs * wq.y, a.z * rs * wq.z, a.w * rs * wq.w));
@@ -239,9 +250,13 @@ resid_norm_kernel(float* __restrict__ h, float* __restrict__ y, const XT* __rest
         srow[i] = v;
         ss += v * v;
     }
-    if (!w_pre) return;
-    const float rs = rsqrtf(block_sum(ss, red) / static_cast<float>(W) + eps);
+    if (!out) return;
     OT* o = out + static_cast<long long>(t) * W;
+    if (!w_pre) {
+        for (int i = threadIdx.x; i < W; i += blockDim.x) stf(o, i, srow[i] * out_scale);
+        return;
+    }
+    const float rs = rsqrtf(block_sum(ss, red) / static_cast<float>(W) + eps) * out_scale;
     for (int i = threadIdx.x; i < W; i += blockDim.x) stf(o, i, srow[i] * rs * ldf(w_pre, i));
 }
 
@@ -260,15 +275,34 @@ __global__ void __launch_bounds__(256) gated_act_kernel(const float* __restrict_
     }
 }
 
+// The clamped form: g = min(gate, limit), u = clamp(up, -limit, limit); out = g * sigmoid(alpha g) * (u + shift).
+template <typename XT>
+__global__ void __launch_bounds__(256) gated_act_clamped_kernel(const float* __restrict__ gu, XT* __restrict__ out,
+                                                                long long total, int I, float alpha, float limit,
+                                                                float shift) {
+    pdl_launch_dependents();
+    pdl_wait();
+    for (long long e = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; e < total;
+         e += static_cast<long long>(gridDim.x) * blockDim.x) {
+        const long long t = e / I;
+        const int i = static_cast<int>(e - t * I);
+        const float g = fminf(gu[t * 2 * I + i], limit);
+        const float u = fminf(fmaxf(gu[t * 2 * I + I + i], -limit), limit);
+        stf(out, e, g * sigmoid_f(alpha * g) * (u + shift));
+    }
+}
+
 // ---- gated RMS norm of a mixer's output --------------------------------------------------------------------------
 // mode 0: out = rms(y) * w * sigmoid(g) * scale      (gate after the norm)
 // mode 1: u = y * silu(g); out = rms(u) * w * scale  (gate before the norm)
-// The norm runs over n / groups consecutive elements; grid (T, groups).
+// mode 2: out = rms(y) * w * silu(g) * scale         (silu gate after the norm)
+// The norm runs over n / groups consecutive elements; grid (T, groups). w_shared: one weight vector of n / groups
+// elements for every group instead of n weights.
 template <typename XT, bool VEC>
 __global__ void __launch_bounds__(1024)
 gated_norm_kernel(const float* __restrict__ y, long long ldy, const float* __restrict__ gate, long long ldg,
                   const XT* __restrict__ w, XT* __restrict__ out, long long ldo, int n_group, float eps, int mode,
-                  float scale) {
+                  float scale, int w_shared) {
     extern __shared__ __align__(16) float sgn[];   // VEC: the group's gated values between the two passes
     __shared__ float red[32];
     pdl_launch_dependents();
@@ -277,6 +311,7 @@ gated_norm_kernel(const float* __restrict__ y, long long ldy, const float* __res
     const int c0 = blockIdx.y * n_group;
     const float* yr = y + t * ldy + c0;
     const float* gr = gate + t * ldg + c0;
+    if (!w_shared) w += c0;
     if (VEC) {   // sizes and pitches multiples of 4, pointers 16-byte aligned: four elements per access, one gate pass
         const int n4 = n_group / 4;
         float4* s4 = reinterpret_cast<float4*>(sgn);
@@ -294,11 +329,14 @@ gated_norm_kernel(const float* __restrict__ y, long long ldy, const float* __res
         XT* o = out + t * ldo + c0;
         for (int i = threadIdx.x; i < n4; i += blockDim.x) {
             float4 v = s4[i];
-            const float4 ww = ld4(w + c0, i);
+            const float4 ww = ld4(w, i);
             v.x *= rs * ww.x, v.y *= rs * ww.y, v.z *= rs * ww.z, v.w *= rs * ww.w;
             if (mode == 0) {
                 const float4 g = ld4(gr, i);
                 v.x *= sigmoid_f(g.x), v.y *= sigmoid_f(g.y), v.z *= sigmoid_f(g.z), v.w *= sigmoid_f(g.w);
+            } else if (mode == 2) {
+                const float4 g = ld4(gr, i);
+                v.x *= silu_f(g.x), v.y *= silu_f(g.y), v.z *= silu_f(g.z), v.w *= silu_f(g.w);
             }
             st4(o, i, v);
         }
@@ -315,9 +353,9 @@ gated_norm_kernel(const float* __restrict__ y, long long ldy, const float* __res
     for (int i = threadIdx.x; i < n_group; i += blockDim.x) {
         float v = yr[i];
         if (mode == 1)
-            v = v * silu_f(gr[i]) * rs * ldf(w, c0 + i);
+            v = v * silu_f(gr[i]) * rs * ldf(w, i);
         else
-            v = v * rs * ldf(w, c0 + i) * sigmoid_f(gr[i]);
+            v = v * rs * ldf(w, i) * (mode == 2 ? silu_f(gr[i]) : sigmoid_f(gr[i]));
         stf(o, i, v * scale);
     }
 }
@@ -480,6 +518,90 @@ conv_state_update_kernel(const float* __restrict__ in, long long ld, int x_off, 
     }
 }
 
+
+// ---- residual short convolution in front of a mixer ---------------------------------------------------------------------
+// out[t, c] = x[t, c] + sum_j w[c][j] * x[row(t) - (K-1-j), c] (the last tap is the row itself; no bias, no activation):
+// what a mixer reads is its input plus a causal convolution of it. x is the fp32 stream [T, ld]; rows before the step come
+// from conv_state [slots, K-1, C] (atx_conv_state_update keeps it), rows before position 0 are zero. A CTA takes kConvRows
+// consecutive rows x 256 channels; a thread walks its channel down the rows, so an input is fetched from memory once.
+template <typename XT>
+__global__ void __launch_bounds__(256)
+conv_residual_kernel(const float* __restrict__ x, long long ld, const XT* __restrict__ w, const float* __restrict__ conv_state,
+                     XT* __restrict__ out, long long ldo, const int* __restrict__ tok_seq, const int* __restrict__ seq_start,
+                     const int* __restrict__ seq_pos0, const int* __restrict__ seq_slot, int T, int C, int K, int rows_per) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int t0 = blockIdx.x * rows_per;
+    const int c = blockIdx.y * blockDim.x + threadIdx.x;
+    if (c >= C) return;
+    float wt[kConvMaxTaps];
+#pragma unroll
+    for (int j = 0; j < kConvMaxTaps; ++j) wt[j] = j < K ? ldf(w, static_cast<long long>(c) * K + j) : 0.f;
+    for (int r = 0; r < rows_per && t0 + r < T; ++r) {
+        const long long t = t0 + r;
+        const int s = tok_seq[t];
+        if (s < 0) continue;
+        const int i = static_cast<int>(t) - seq_start[s];
+        const int pos0 = seq_pos0[s];
+        const float* st = conv_state + static_cast<long long>(seq_slot[s]) * (K - 1) * C;
+        const float cur = x[t * ld + c];
+        float acc = cur;
+#pragma unroll
+        for (int j = 0; j < kConvMaxTaps; ++j) {
+            if (j >= K) break;
+            const int rel = i - (K - 1 - j);
+            float v = 0.f;
+            if (j == K - 1)
+                v = cur;
+            else if (rel >= 0)
+                v = x[(t - i + rel) * ld + c];   // an earlier row of the same portion (L1 / L2: the rows above in this tile)
+            else if (pos0 + rel >= 0)
+                v = st[static_cast<long long>(K - 1 + rel) * C + c];
+            acc = fmaf(wt[j], v, acc);
+        }
+        stf(out + t * ldo, c, acc);
+    }
+}
+
+// ---- data-dependent decay per channel through a low-rank projection -------------------------------------------------
+// z[t, c] = b[c] + sum_r A[c, r] * lo[t, r];  out[t, c] = log(sigmoid(z)^(1/tau)) = -softplus(-z) / tau  (fp32, <= 0).
+// lo: the fp32 output of the first (narrow) projection, R columns at pitch ld. One CTA per row tile of 8 rows; the narrow
+// rows sit in shared memory and a thread owns a channel (its R weights in registers when R <= 32).
+template <typename XT>
+__global__ void __launch_bounds__(256)
+lowrank_logdecay_kernel(const float* __restrict__ lo, long long ld, const XT* __restrict__ A, const XT* __restrict__ b,
+                        float* __restrict__ out, long long ldo, int T, int C, int R, float inv_tau) {
+    extern __shared__ __align__(16) float slo[];   // [8][R]
+    pdl_launch_dependents();
+    pdl_wait();
+    const int t0 = blockIdx.x * 8;
+    const int rows = min(8, T - t0);
+    for (int e = threadIdx.x; e < rows * R; e += blockDim.x) {
+        const int i = e / R, r = e - i * R;
+        slo[e] = lo[static_cast<long long>(t0 + i) * ld + r];
+    }
+    __syncthreads();
+    for (int c = blockIdx.y * blockDim.x + threadIdx.x; c < C; c += gridDim.y * blockDim.x) {
+        float acc[8];
+        const float bias = b ? ldf(b, c) : 0.f;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) acc[i] = bias;
+        for (int r = 0; r < R; ++r) {
+            const float a = ldf(A, static_cast<long long>(c) * R + r);
+#pragma unroll
+            for (int i = 0; i < 8; ++i)
+                if (i < rows) acc[i] = fmaf(a, slo[i * R + r], acc[i]);
+        }
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            if (i >= rows) break;
+            const float z = acc[i];
+            // log sigmoid(z) = -softplus(-z) = min(z, 0) - log1p(exp(-|z|)), exact for every z
+            out[static_cast<long long>(t0 + i) * ldo + c] = (fminf(z, 0.f) - log1pf(expf(-fabsf(z)))) * inv_tau;
+        }
+    }
+}
+
 // packed fp32 pairs (sm_100 FFMA2 / FMUL2): two state rows per instruction
 typedef unsigned long long f32x2;
 __device__ __forceinline__ f32x2 pk2(float lo, float hi) {
@@ -506,12 +628,14 @@ __device__ __forceinline__ f32x2 mul2(f32x2 a, f32x2 b) {
 //   a_t = decay_head[h] or decay_tok[t, h];  c_t = kscale_tok[t, h] or 1;  d = skip[h] or 0;
 //   q and k of head h are read from group h / (H / G) (G = H: a q/k per head), v from head h;
 //   act = 1 applies silu to q, k and v as they are read.
+//   CH: the decay acts per key channel instead, a_t[d] = exp(ldecay_chan[t, h D + d]) (logarithms given, pitch ldc), and q
+//   is multiplied by qscale as it is read.
 // One CTA owns a V-tile of one head of one sequence and walks the sequence's rows in order. A thread keeps DS rows of
 // one column of S in registers for the whole walk (the state is read once and written once per step); rows are staged
 // through shared memory kChunk at a time, and the partial dot products of the D-slices are summed per chunk.
 constexpr int kRecChunk = 16;
 
-template <int DS, bool FULL>   // FULL: D is a multiple of DS (no partial slice) and rows of q / k are 16-byte aligned
+template <int DS, bool FULL, bool CH = false>   // FULL: D is a multiple of DS (no partial slice) and rows of q / k are 16-byte aligned
 __global__ void __launch_bounds__(256, DS == 32 ? 2 : 1)
 linear_recurrence_kernel(const float* __restrict__ q, long long ldq, const float* __restrict__ k, long long ldk,
                          const float* __restrict__ v, long long ldv, int H, int G, int D, int V,
@@ -519,7 +643,8 @@ linear_recurrence_kernel(const float* __restrict__ q, long long ldq, const float
                          const float* __restrict__ kscale_tok, const float* __restrict__ skip, int act,
                          float* __restrict__ state, float* __restrict__ y, long long ldy,
                          const int* __restrict__ seq_start, const int* __restrict__ seq_count,
-                         const int* __restrict__ seq_pos0, const int* __restrict__ seq_slot, int VT, int DG) {
+                         const int* __restrict__ seq_pos0, const int* __restrict__ seq_slot, int VT, int DG,
+                         const float* __restrict__ ldecay_chan = nullptr, long long ldc = 0, float qscale = 1.f) {
     extern __shared__ __align__(16) float sm[];
     pdl_launch_dependents();
     pdl_wait();
@@ -537,6 +662,7 @@ linear_recurrence_kernel(const float* __restrict__ q, long long ldq, const float
     float* sv = sk + kRecChunk * D;            // [kRecChunk][VT]
     float* sa = sv + kRecChunk * VT;           // [kRecChunk]
     float* sp = sa + kRecChunk;                // [kRecChunk][DG][VT] partial outputs
+    float* sd = sp + kRecChunk * DG * VT;      // CH: [kRecChunk][D] decay factors per key channel
     float S[DS];
     float* st = state + ((static_cast<long long>(seq_slot[s]) * H + h) * D) * V;
     const bool fresh = seq_pos0[s] == 0;
@@ -555,6 +681,10 @@ linear_recurrence_kernel(const float* __restrict__ q, long long ldq, const float
                 kv = silu_f(kv);
             }
             if (kscale_tok) kv *= kscale_tok[row * H + h];
+            if (CH) {
+                qv *= qscale;
+                sd[i * D + d] = expf(ldecay_chan[row * ldc + static_cast<long long>(h) * D + d]);
+            }
             sq[i * D + d] = qv;
             sk[i * D + d] = kv;
         }
@@ -565,28 +695,37 @@ linear_recurrence_kernel(const float* __restrict__ q, long long ldq, const float
             if (act) vv = silu_f(vv);
             sv[i * VT + j] = vv;
         }
-        for (int i = threadIdx.x; i < cn; i += blockDim.x)
-            sa[i] = decay_tok ? decay_tok[(r0 + c0 + i) * H + h] : decay_head[h];
+        if (!CH)
+            for (int i = threadIdx.x; i < cn; i += blockDim.x)
+                sa[i] = decay_tok ? decay_tok[(r0 + c0 + i) * H + h] : decay_head[h];
         __syncthreads();
         if (live) {
             for (int i = 0; i < cn; ++i) {
-                const float a = sa[i], vv = sv[i * VT + tv];
+                const float a = CH ? 1.f : sa[i], vv = sv[i * VT + tv];
                 const float* qi = sq + i * D + d0;
                 const float* ki = sk + i * D + d0;
+                const float* di = sd + i * D + d0;
                 float acc = 0.f;
                 if (FULL) {
                     // state rows in pairs: S2 = a2 * S2 + k2 * v2; acc2 += S2 * q2  (three packed operations per pair),
                     // four independent accumulators so that the dot product is not one dependent chain
                     const ulonglong2* q4 = reinterpret_cast<const ulonglong2*>(qi);
                     const ulonglong2* k4 = reinterpret_cast<const ulonglong2*>(ki);
+                    const ulonglong2* d4 = reinterpret_cast<const ulonglong2*>(di);
                     const f32x2 a2 = pk2(a, a), v2 = pk2(vv, vv);
                     f32x2 ac[4] = {0ull, 0ull, 0ull, 0ull};
 #pragma unroll
                     for (int d = 0; d < DS / 4; ++d) {
                         const ulonglong2 kk = k4[d], qq = q4[d];
                         f32x2 s0 = pk2(S[4 * d], S[4 * d + 1]), s1 = pk2(S[4 * d + 2], S[4 * d + 3]);
-                        s0 = fma2(a2, s0, mul2(kk.x, v2));
-                        s1 = fma2(a2, s1, mul2(kk.y, v2));
+                        if (CH) {
+                            const ulonglong2 dd = d4[d];
+                            s0 = fma2(dd.x, s0, mul2(kk.x, v2));
+                            s1 = fma2(dd.y, s1, mul2(kk.y, v2));
+                        } else {
+                            s0 = fma2(a2, s0, mul2(kk.x, v2));
+                            s1 = fma2(a2, s1, mul2(kk.y, v2));
+                        }
                         ac[(2 * d) & 3] = fma2(s0, qq.x, ac[(2 * d) & 3]);
                         ac[(2 * d + 1) & 3] = fma2(s1, qq.y, ac[(2 * d + 1) & 3]);
                         upk2(s0, S[4 * d], S[4 * d + 1]);
@@ -602,7 +741,7 @@ linear_recurrence_kernel(const float* __restrict__ q, long long ldq, const float
 #pragma unroll
                     for (int d = 0; d < DS; ++d) {
                         if (d0 + d < D) {
-                            S[d] = fmaf(a, S[d], ki[d] * vv);
+                            S[d] = fmaf(CH ? di[d] : a, S[d], ki[d] * vv);
                             acc = fmaf(S[d], qi[d], acc);
                         }
                     }
@@ -690,11 +829,19 @@ int atx_resid_norm(float* h, float* y, const void* w_post, const void* vec, cons
 int atx_resid_norm_scaled(float* h, float* y, const void* w_post, const void* post_scale, const void* vec,
                           const void* w_pre, void* out, int out_f32, const int* rows, int T, int W, float eps, int zero_y,
                           void* zero_ptr, long long zero_bytes, int dtype, int flags, atx_stream_t stream) {
+    ATX_REQUIRE((w_pre == nullptr) == (out == nullptr), "atx_resid_norm: w_pre and out come together");
+    return atx_resid_norm_out(h, y, w_post, post_scale, vec, w_pre, out, out_f32, 1.f, rows, T, W, eps, zero_y, zero_ptr,
+                              zero_bytes, dtype, flags, stream);
+}
+
+int atx_resid_norm_out(float* h, float* y, const void* w_post, const void* post_scale, const void* vec, const void* w_pre,
+                       void* out, int out_f32, float out_scale, const int* rows, int T, int W, float eps, int zero_y,
+                       void* zero_ptr, long long zero_bytes, int dtype, int flags, atx_stream_t stream) {
     ATX_REQUIRE(h, "atx_resid_norm: null pointer");
     ATX_REQUIRE(!post_scale || w_post, "atx_resid_norm: post_scale needs y and w_post");
     ATX_REQUIRE(T > 0 && W > 0 && W <= 12288, "atx_resid_norm: bad shape T=%d W=%d (W <= 12288)", T, W);
     ATX_REQUIRE((y == nullptr) == (w_post == nullptr), "atx_resid_norm: y and w_post come together");
-    ATX_REQUIRE((w_pre == nullptr) == (out == nullptr), "atx_resid_norm: w_pre and out come together");
+    ATX_REQUIRE(!w_pre || out, "atx_resid_norm: w_pre needs out");
     ATX_REQUIRE(zero_bytes >= 0 && zero_bytes % 16 == 0 && (zero_bytes == 0 || zero_ptr) && !(zero_y && rows),
                 "atx_resid_norm: zero_bytes=%lld must be a non-negative multiple of 16 with a buffer; zero_y not with rows",
                 zero_bytes);
@@ -716,7 +863,7 @@ int atx_resid_norm_scaled(float* h, float* y, const void* w_post, const void* po
                                &cfg, resid_norm_kernel<XT, OT_, VEC_>, h, y, reinterpret_cast<const XT*>(w_post),         \
                                reinterpret_cast<const XT*>(post_scale), reinterpret_cast<const XT*>(vec),                 \
                                reinterpret_cast<const XT*>(w_pre), reinterpret_cast<OT_*>(out), rows, T, W, eps, zero_y,  \
-                               reinterpret_cast<uint4*>(zero_ptr), zv)))
+                               reinterpret_cast<uint4*>(zero_ptr), zv, out_scale)))
     if (out_f32) {
         if (v4)
             ATX_RESID(float, true);
@@ -749,11 +896,36 @@ int atx_gated_act(const float* gu, void* out, int T, int I, int dtype, int flags
     return ATX_OK;
 }
 
+int atx_gated_act_clamped(const float* gu, void* out, int T, int I, float alpha, float limit, float shift, int dtype,
+                          int flags, atx_stream_t stream) {
+    ATX_REQUIRE(gu && out, "atx_gated_act_clamped: null pointer");
+    ATX_REQUIRE(T > 0 && I > 0 && limit > 0.f, "atx_gated_act_clamped: bad arguments T=%d I=%d limit=%g", T, I, limit);
+    const long long total = static_cast<long long>(T) * I;
+    long long blocks = (total + 255) / 256;
+    const long long cap = static_cast<long long>(num_sms()) * 16;
+    if (blocks > cap) blocks = cap;
+    cudaLaunchConfig_t cfg = {};
+    cudaLaunchAttribute attr[1];
+    cfg.gridDim = dim3(static_cast<unsigned>(blocks));
+    cfg.blockDim = dim3(256);
+    cfg.stream = reinterpret_cast<cudaStream_t>(stream);
+    set_pdl2(cfg, attr, flags);
+    ATX_DISPATCH_XT(dtype, ATX_CUDA(cudaLaunchKernelEx(&cfg, gated_act_clamped_kernel<XT>, gu, reinterpret_cast<XT*>(out),
+                                                       total, I, alpha, limit, shift)));
+    return ATX_OK;
+}
+
 int atx_gated_norm(const float* y, long long ldy, const float* gate, long long ldg, const void* w, void* out,
                    long long ldo, int T, int n, int groups, float eps, int mode, float scale, int dtype, int flags,
                    atx_stream_t stream) {
+    return atx_gated_norm_groups(y, ldy, gate, ldg, w, 0, out, ldo, T, n, groups, eps, mode, scale, dtype, flags, stream);
+}
+
+int atx_gated_norm_groups(const float* y, long long ldy, const float* gate, long long ldg, const void* w, int w_shared,
+                          void* out, long long ldo, int T, int n, int groups, float eps, int mode, float scale, int dtype,
+                          int flags, atx_stream_t stream) {
     ATX_REQUIRE(y && gate && w && out, "atx_gated_norm: null pointer");
-    ATX_REQUIRE(T > 0 && n > 0 && groups > 0 && n % groups == 0 && (mode == 0 || mode == 1),
+    ATX_REQUIRE(T > 0 && n > 0 && groups > 0 && n % groups == 0 && mode >= 0 && mode <= 2,
                 "atx_gated_norm: bad arguments T=%d n=%d groups=%d mode=%d", T, n, groups, mode);
     cudaLaunchConfig_t cfg = {};
     cudaLaunchAttribute attr[1];
@@ -768,7 +940,7 @@ int atx_gated_norm(const float* y, long long ldy, const float* gate, long long l
 #define ATX_GNORM(VEC_)                                                                                                  \
     ATX_DISPATCH_XT(dtype, ATX_CUDA(cudaLaunchKernelEx(&cfg, gated_norm_kernel<XT, VEC_>, y, ldy, gate, ldg,             \
                                                        reinterpret_cast<const XT*>(w), reinterpret_cast<XT*>(out), ldo,  \
-                                                       ng, eps, mode, scale)))
+                                                       ng, eps, mode, scale, w_shared)))
     if (v4) {
         cfg.dynamicSmemBytes = static_cast<size_t>(ng) * 4;
         if (ng * 4 > 48 * 1024) {
@@ -877,7 +1049,7 @@ int atx_linear_recurrence(const float* q, long long ldq, const float* k, long lo
                                           cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));          \
         ATX_CUDA(cudaLaunchKernelEx(&cfg, linear_recurrence_kernel<DS_, FULL_>, q, ldq, k, ldk, v, ldv, H, G, D, V,       \
                                     decay_head, decay_tok, kscale_tok, skip, act, state, y, ldy, seq_start, seq_count,   \
-                                    seq_pos0, seq_slot, VT, DG));                                                         \
+                                    seq_pos0, seq_slot, VT, DG, static_cast<const float*>(nullptr), 0LL, 1.f)); \
     } while (0)
     if (DS == 32 && full)
         ATX_REC_LAUNCH(32, true);
@@ -888,6 +1060,92 @@ int atx_linear_recurrence(const float* q, long long ldq, const float* k, long lo
     else
         ATX_REC_LAUNCH(64, false);
 #undef ATX_REC_LAUNCH
+    return ATX_OK;
+}
+
+int atx_conv_residual(const float* x, long long ld, const void* w, const float* conv_state, void* out, long long ldo,
+                      const int* tok_seq, const int* seq_start, const int* seq_pos0, const int* seq_slot, int T, int C,
+                      int K, int dtype, int flags, atx_stream_t stream) {
+    ATX_REQUIRE(x && w && out && tok_seq && seq_start && seq_pos0 && seq_slot && (K == 1 || conv_state),
+                "atx_conv_residual: null pointer");
+    ATX_REQUIRE(T > 0 && C > 0 && K >= 1 && K <= kConvMaxTaps, "atx_conv_residual: bad shape T=%d C=%d taps=%d (<= %d)", T, C,
+                K, kConvMaxTaps);
+    const int rows_per = T >= 256 ? kConvRows : 1;   // few rows (decode): a CTA per row and 256 channels
+    cudaLaunchConfig_t cfg = {};
+    cudaLaunchAttribute attr[1];
+    cfg.gridDim = dim3((T + rows_per - 1) / rows_per, (C + 255) / 256);
+    cfg.blockDim = dim3(256);
+    cfg.stream = reinterpret_cast<cudaStream_t>(stream);
+    set_pdl2(cfg, attr, flags);
+    ATX_DISPATCH_XT(dtype, ATX_CUDA(cudaLaunchKernelEx(&cfg, conv_residual_kernel<XT>, x, ld, reinterpret_cast<const XT*>(w),
+                                                       conv_state, reinterpret_cast<XT*>(out), ldo, tok_seq, seq_start,
+                                                       seq_pos0, seq_slot, T, C, K, rows_per)));
+    return ATX_OK;
+}
+
+int atx_lowrank_logdecay(const float* lo, long long ld, const void* A, const void* b, float* out, long long ldo, int T,
+                         int C, int R, float tau, int dtype, int flags, atx_stream_t stream) {
+    ATX_REQUIRE(lo && A && out, "atx_lowrank_logdecay: null pointer");
+    ATX_REQUIRE(T > 0 && C > 0 && R > 0 && R <= 4096 && tau > 0.f, "atx_lowrank_logdecay: bad arguments T=%d C=%d R=%d tau=%g",
+                T, C, R, tau);
+    cudaLaunchConfig_t cfg = {};
+    cudaLaunchAttribute attr[1];
+    cfg.gridDim = dim3((T + 7) / 8, (C + 255) / 256);
+    cfg.blockDim = dim3(256);
+    cfg.dynamicSmemBytes = sizeof(float) * 8 * static_cast<size_t>(R);
+    cfg.stream = reinterpret_cast<cudaStream_t>(stream);
+    set_pdl2(cfg, attr, flags);
+    const float inv_tau = 1.f / tau;
+    ATX_DISPATCH_XT(dtype, ATX_CUDA(cudaLaunchKernelEx(&cfg, lowrank_logdecay_kernel<XT>, lo, ld,
+                                                       reinterpret_cast<const XT*>(A), reinterpret_cast<const XT*>(b), out,
+                                                       ldo, T, C, R, inv_tau)));
+    return ATX_OK;
+}
+
+int atx_gated_linear_recurrence(const float* q, long long ldq, const float* k, long long ldk, const float* v, long long ldv,
+                                const float* ldecay, long long ldc, int H, int D, int V, float qscale, float* state,
+                                float* y, long long ldy, const int* seq_start, const int* seq_count, const int* seq_pos0,
+                                const int* seq_slot, int n_seqs, int flags, atx_stream_t stream) {
+    ATX_REQUIRE(q && k && v && ldecay && state && y && seq_start && seq_count && seq_pos0 && seq_slot,
+                "atx_gated_linear_recurrence: null pointer");
+    ATX_REQUIRE(n_seqs > 0 && H > 0 && D > 0 && V > 0 && D <= 512,
+                "atx_gated_linear_recurrence: bad shape n_seqs=%d H=%d D=%d V=%d (D <= 512)", n_seqs, H, D, V);
+    const int DS = D > 256 ? 64 : 32;
+    const int DG = (D + DS - 1) / DS;
+    int VT = (256 / DG) / 32 * 32;
+    if (VT < 32) VT = 32;
+    const int v32 = (V + 31) / 32 * 32;
+    if (VT > v32) VT = v32;
+    const int threads = VT * DG;
+    const size_t smem = sizeof(float) * (static_cast<size_t>(kRecChunk) * (3 * D + VT + 1 + DG * VT));
+    cudaLaunchConfig_t cfg = {};
+    cudaLaunchAttribute attr[1];
+    cfg.gridDim = dim3(n_seqs, H, (V + VT - 1) / VT);
+    cfg.blockDim = dim3(threads);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = reinterpret_cast<cudaStream_t>(stream);
+    set_pdl2(cfg, attr, flags);
+    ATX_REQUIRE(smem <= 160 * 1024, "atx_gated_linear_recurrence: D=%d needs %zu bytes of shared memory", D, smem);
+    const bool full = D % DS == 0 && D % 4 == 0;
+    const float* none = nullptr;
+#define ATX_GREC_LAUNCH(DS_, FULL_)                                                                                      \
+    do {                                                                                                                  \
+        if (smem > 48 * 1024)                                                                                             \
+            ATX_CUDA(cudaFuncSetAttribute(linear_recurrence_kernel<DS_, FULL_, true>,                                     \
+                                          cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));          \
+        ATX_CUDA(cudaLaunchKernelEx(&cfg, linear_recurrence_kernel<DS_, FULL_, true>, q, ldq, k, ldk, v, ldv, H, H, D, V, \
+                                    none, none, none, none, 0, state, y, ldy, seq_start, seq_count, seq_pos0, seq_slot,  \
+                                    VT, DG, ldecay, ldc, qscale));                                                        \
+    } while (0)
+    if (DS == 32 && full)
+        ATX_GREC_LAUNCH(32, true);
+    else if (DS == 32)
+        ATX_GREC_LAUNCH(32, false);
+    else if (full)
+        ATX_GREC_LAUNCH(64, true);
+    else
+        ATX_GREC_LAUNCH(64, false);
+#undef ATX_GREC_LAUNCH
     return ATX_OK;
 }
 

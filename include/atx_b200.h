@@ -488,6 +488,44 @@ int atx_moe_combine(float* y, const float* ye, long long lde, const void* x, con
                     const int* slot_of, const float* shared_gate, long long ldsg, int T, int W, int top, int E, int dtype,
                     int flags, atx_stream_t stream);
 
+/* ---- Further mechanisms: a norm behind a sublayer only, a residual short convolution in front of a mixer, a recurrence
+ * whose state decays per key channel, clamped gates, renormalised expert weights. (Napuzen is built from these; every
+ * constant is an argument.) */
+
+/* atx_resid_norm_scaled where the consumer may read the stream without a norm: w_pre == NULL with out != NULL writes
+ * out[t] = h[r] * out_scale (element type, or fp32 with out_f32); with w_pre, out[t] = rms(h[r]) * w_pre * out_scale. */
+int atx_resid_norm_out(float* h, float* y, const void* w_post, const void* post_scale, const void* vec, const void* w_pre,
+                       void* out, int out_f32, float out_scale, const int* rows, int T, int W, float eps, int zero_y,
+                       void* zero_ptr, long long zero_bytes, int dtype, int flags, atx_stream_t stream);
+/* out[t, i] = g * sigmoid(alpha * g) * (u + shift), g = min(gu[t, i], limit), u = clamp(gu[t, I + i], -limit, limit). */
+int atx_gated_act_clamped(const float* gu, void* out, int T, int I, float alpha, float limit, float shift, int dtype,
+                          int flags, atx_stream_t stream);
+/* atx_gated_norm with mode 2: out = rms(y) * w * silu(gate) * scale, and with w_shared != 0: w holds n / groups weights
+ * that every group uses (a norm per head with one weight vector for all heads). */
+int atx_gated_norm_groups(const float* y, long long ldy, const float* gate, long long ldg, const void* w, int w_shared,
+                          void* out, long long ldo, int T, int n, int groups, float eps, int mode, float scale, int dtype,
+                          int flags, atx_stream_t stream);
+/* out[t, c] = x[t, c] + sum_j w[c, j] * x[t - (K - 1 - j), c] over the rows of t's sequence (K taps, at most 8; w [C, K] of
+ * the element type; no bias, no activation): x fp32 [T, ld], out of the element type [T, ldo]. The K - 1 rows before a
+ * step come from conv_state [slots, K - 1, C] fp32, which atx_conv_state_update(x, ld, 0, ...) refreshes after this call;
+ * rows before position 0 are zero. Rows with tok_seq < 0 are skipped. */
+int atx_conv_residual(const float* x, long long ld, const void* w, const float* conv_state, void* out, long long ldo,
+                      const int* tok_seq, const int* seq_start, const int* seq_pos0, const int* seq_slot, int T, int C,
+                      int K, int dtype, int flags, atx_stream_t stream);
+/* out[t, c] = log(sigmoid(b[c] + sum_r A[c, r] * lo[t, r])) / tau, fp32: the logarithm of a decay factor in (0, 1) per
+ * channel from a narrow projection lo [T, ld] fp32 (R columns); A [C, R], b [C] (nullable) of the element type. */
+int atx_lowrank_logdecay(const float* lo, long long ld, const void* A, const void* b, float* out, long long ldo, int T,
+                         int C, int R, float tau, int dtype, int flags, atx_stream_t stream);
+/* atx_linear_recurrence with a decay per key channel: S_t = diag(a_t) S_(t-1) + k_t v_t^T, y_t = S_t^T (qscale q_t), with
+ * a_t[d] = exp(ldecay[t, h * D + d]) (pitch ldc). State fp32 [slots, H, D, V]; q, k [., H * D], v, y [., H * V] fp32. */
+int atx_gated_linear_recurrence(const float* q, long long ldq, const float* k, long long ldk, const float* v, long long ldv,
+                                const float* ldecay, long long ldc, int H, int D, int V, float qscale, float* state,
+                                float* y, long long ldy, const int* seq_start, const int* seq_count, const int* seq_pos0,
+                                const int* seq_slot, int n_seqs, int flags, atx_stream_t stream);
+/* atx_moe_route with normalize != 0: wgt = score / (sum of the chosen scores + 1e-20) * scale. */
+int atx_moe_route_opts(const float* logits, long long ld, const float* correction, int R, int top, float scale,
+                       int normalize, int* sel, float* wgt, int T, int flags, atx_stream_t stream);
+
 #ifdef __cplusplus
 }
 #endif
