@@ -20,6 +20,7 @@ GEMM_ADD_F32 = 1
 GEMM_STORE_BF16 = 2
 GEMM_SWIGLU_BF16 = 3
 GEMM_RELU2_BF16 = 4
+GEMM_GLU_CLAMP_BF16 = 5
 FLAG_PDL = 1
 FLAG_ORDERED = 2   # atx_gemm_run ADD_F32, T <= 64: fixed-order split-K (bit-reproducible)
 FLAG_ADD_BF16 = 4  # atx_rmsnorm: the `add` buffer is bf16
@@ -47,7 +48,7 @@ EXPORTS = [
     "atx_moe_route", "atx_moe_tile_rows", "atx_moe_plan", "atx_moe_expert_gemm", "atx_moe_combine", "atx_moe_gather_rows",
     "atx_gemm_run_grouped", "atx_gemm_grouped_tile_rows",
     "atx_resid_norm_out", "atx_gated_act_clamped", "atx_gated_norm_groups", "atx_conv_residual", "atx_lowrank_logdecay",
-    "atx_gated_linear_recurrence", "atx_moe_route_opts",
+    "atx_gated_linear_recurrence", "atx_moe_route_opts", "atx_gemm_plan_set_gate",
 ]
 ATTN_SOFTMAX = 0
 ATTN_SIGMOID = 1
@@ -201,6 +202,7 @@ def load() -> C.CDLL:
     lib.atx_lowrank_logdecay.argtypes = [vp, i64, vp, vp, vp, i64, i32, i32, i32, f32, i32, i32, vp]
     lib.atx_gated_linear_recurrence.argtypes = [vp, i64, vp, i64, vp, i64, vp, i64, i32, i32, i32, f32, vp, vp, i64, vp, vp,
                                                 vp, vp, i32, i32, vp]
+    lib.atx_gemm_plan_set_gate.argtypes = [vp, f32, f32, f32]
     lib.atx_moe_route_opts.argtypes = [vp, i64, vp, i32, i32, f32, i32, vp, vp, i32, i32, vp]
     for name in EXPORTS:  # fail at load time, not at first use, if the build is stale
         getattr(lib, name)
@@ -242,10 +244,14 @@ class GemmPlan:
                                            x_buf.stride(0)))
         self._h = h
 
+    def set_gate(self, alpha: float, limit: float, shift: float) -> None:
+        """Constants of GEMM_GLU_CLAMP_BF16: out = g sigmoid(alpha g) (u + shift), g = min(gate, limit), u = clamp(up, +-limit)."""
+        _check(load().atx_gemm_plan_set_gate(self._h, alpha, limit, shift))
+
     def run(self, out: torch.Tensor, T: int, mode: int, splits: int = 0, flags: int = 0) -> None:
         _dev(out)
-        want = torch.bfloat16 if mode in (GEMM_STORE_BF16, GEMM_SWIGLU_BF16, GEMM_RELU2_BF16) else torch.float32
-        cols = self.N // 2 if mode == GEMM_SWIGLU_BF16 else self.N
+        want = torch.bfloat16 if mode in (GEMM_STORE_BF16, GEMM_SWIGLU_BF16, GEMM_RELU2_BF16, GEMM_GLU_CLAMP_BF16) else torch.float32
+        cols = self.N // 2 if mode in (GEMM_SWIGLU_BF16, GEMM_GLU_CLAMP_BF16) else self.N
         assert out.dtype == want and out.dim() == 2 and out.shape[1] >= cols and out.shape[0] >= T
         _check(load().atx_gemm_run(self._h, out.data_ptr(), out.stride(0), T, mode, splits, flags, _stream()))
 

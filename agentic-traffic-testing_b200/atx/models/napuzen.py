@@ -290,7 +290,8 @@ class _Layer:
         self.dq_norm = self.dkv_norm = self.w_uq = None               # latent bottlenecks
         self.w_ukt = self.w_uv = None        # [heads * kv_rank, dim] (W_uk per head, transposed), [heads * vdim, kv_rank]
         self.ff = ""                         # "", "dense", "moe"
-        self.w_gu = self.w_down = None       # dense: [gate rows ; up rows]
+        self.w_gu = self.w_down = None       # dense: [gate rows ; up rows], or in blocks of 64 (gu_interleaved)
+        self.gu_interleaved = False
         self.w_router = None                 # [experts (+ 1: the shared expert's gate), width]
         self.w_egu = self.w_edown = None     # [experts, 2 ff, width], [experts, width, ff]
         self.w_sgu = self.w_sdown = None     # shared expert
@@ -406,7 +407,7 @@ class Weights:
                 f = p + "mlp."
                 if mlp.get("kind", "dense") == "dense":
                     l.ff = "dense"
-                    l.w_gu, l.w_down = dev(torch.cat([get(f + "gate"), get(f + "up")], 0)), dev(get(f + "down"))
+                    (l.w_gu, l.gu_interleaved), l.w_down = gate_up(get(f + "gate"), get(f + "up")), dev(get(f + "down"))
                 else:
                     l.ff = "moe"
                     E, Fe = int(mlp["router"]["experts"]), int(mlp["expert"]["ff"])
@@ -524,6 +525,8 @@ class Program:
                 d["uq"] = _Linear(lib, l.w_uq, view(self.cq_flat, l.w_uq.shape[1]), self.dt)
             if l.ff == "dense":
                 d["gu"] = _Linear(lib, l.w_gu, self.xn, self.dt)
+                if l.gu_interleaved:     # the clamps and the gate run in the GEMM's epilogue
+                    d["gu"].plan.set_gate(GLU_ALPHA, float(spec["mlp"]["limit"]), GLU_SHIFT)
                 d["down"] = _Linear(lib, l.w_down, view(self.act_flat, l.w_down.shape[1]), self.dt)
             elif l.ff == "moe":
                 d["router"] = _Linear(lib, l.w_router, self.xn, self.dt)
@@ -745,12 +748,18 @@ class Program:
             if l.ff == "dense":
                 mlp = spec["mlp"]
                 F = l.w_down.shape[1]
-                acc = lin["gu"].accumulates(T)
-                resid(xn, zero_ptr=up if acc else None, zero_bytes=(T * 2 * F * 4 + 15) // 16 * 16 if acc else 0)
-                lin["gu"].run(up, 2 * F, T, fl, st, zeroed=acc)
-                ck(lib.atx_gated_act_clamped(up, act, T, F, GLU_ALPHA, float(mlp["limit"]), GLU_SHIFT, dt, fl, st))
+                if l.gu_interleaved:
+                    resid(xn)
+                    lin["gu"].run(act, F, T, fl, st, mode=_cabi.GEMM_GLU_CLAMP_BF16)
+                    n += 1
+                else:
+                    acc = lin["gu"].accumulates(T)
+                    resid(xn, zero_ptr=up if acc else None, zero_bytes=(T * 2 * F * 4 + 15) // 16 * 16 if acc else 0)
+                    lin["gu"].run(up, 2 * F, T, fl, st, zeroed=acc)
+                    ck(lib.atx_gated_act_clamped(up, act, T, F, GLU_ALPHA, float(mlp["limit"]), GLU_SHIFT, dt, fl, st))
+                    n += 2
                 lin["down"].run(y, W, T, fl, st, zeroed=small)
-                n += 3
+                n += 1
                 pending = l.norm2.data_ptr()
             elif l.ff == "moe":
                 mlp = spec["mlp"]

@@ -24,6 +24,22 @@
 
 namespace atx {
 
+// The gated epilogues: ATX_GEMM_SWIGLU_BF16 = silu(gate) * up; ATX_GEMM_GLU_CLAMP_BF16 = g sigmoid(alpha g) (u + shift) with
+// g = min(gate, limit), u = clamp(up, -limit, limit) (alpha, limit, shift: atx_gemm_plan_set_gate). Same tile layout.
+struct GateParams {
+    float alpha, limit, shift;
+};
+__host__ __device__ __forceinline__ bool is_glu(int mode) {
+    return mode == ATX_GEMM_SWIGLU_BF16 || mode == ATX_GEMM_GLU_CLAMP_BF16;
+}
+__device__ __forceinline__ float glu_value(float g, float u, int mode, const GateParams& gp) {
+    if (mode == ATX_GEMM_SWIGLU_BF16) return g / (1.f + expf(-g)) * u;
+    g = fminf(g, gp.limit);
+    u = fminf(fmaxf(u, -gp.limit), gp.limit);
+    return g / (1.f + expf(-gp.alpha * g)) * (u + gp.shift);
+}
+
+
 constexpr int kBM = 128;  // weight rows per CTA (UMMA M)
 constexpr int kBK = 64;   // K elements per stage (= one 128-byte swizzle row of bf16)
 constexpr int kUK = 16;   // UMMA K for 16-bit inputs
@@ -63,7 +79,7 @@ template <int TN>
 __global__ void __launch_bounds__(kGemmThreads)
 gemm_wt_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmX,
                void* __restrict__ out, long long ldo, int T, int N, int kb_total, int kb_per_split,
-               int mode_in, int w_evict_first, int stages) {
+               int mode_in, int w_evict_first, int stages, GateParams gate_params) {
     const int mode = mode_in & 0xff;
     const bool ordered = (mode_in & 0x100) != 0;   // ATX_FLAG_ORDERED: split-K summed in a fixed order (below)
     // `stages` (<= Cfg::kStages) is the ring depth actually used: CTAs with few k-blocks get a smaller
@@ -175,7 +191,7 @@ gemm_wt_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
         mbar_wait(accum_bar, 0);
         tc_fence_after();
         pdl_wait();  // `out` may be the residual stream written by the upstream grid
-        const bool nonlinear = mode == ATX_GEMM_SWIGLU_BF16 || mode == ATX_GEMM_RELU2_BF16 || ordered;
+        const bool nonlinear = is_glu(mode) || mode == ATX_GEMM_RELU2_BF16 || ordered;
         if (nonlinear && gridDim.z > 1) {
             // Split-K with a nonlinear epilogue (or with ATX_FLAG_ORDERED, where the order of the additions must
             // not depend on timing): the gridDim.z CTAs of this tile form ONE thread-block
@@ -220,7 +236,7 @@ gemm_wt_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
         }
         if (nonlinear && blockIdx.z != 0) {
             // cluster peer: its sum now lives in the leader's accumulator
-        } else if (mode == ATX_GEMM_SWIGLU_BF16) {
+        } else if (is_glu(mode)) {
             // Rows [0,64) of this tile are gate features, rows [64,128) the matching up features
             // (weights interleaved in 64-row groups at load time): act = silu(gate) * up, bf16.
             // The halves cross between warps 0-1 (gate lanes) and warps 2-3 (up lanes) through the
@@ -263,7 +279,7 @@ gemm_wt_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
                         const float mine = __uint_as_float(v[j]), other = sx[(c + j) * 64 + i];
                         const float g = gate_warp ? mine : other, u = gate_warp ? other : mine;
                         if (ok && t < T)
-                            o[static_cast<long long>(t) * ldo + col] = __float2bfloat16_rn(g / (1.f + expf(-g)) * u);
+                            o[static_cast<long long>(t) * ldo + col] = __float2bfloat16_rn(glu_value(g, u, mode, gate_params));
                     }
                 }
             }
@@ -366,7 +382,7 @@ __global__ void __launch_bounds__(kPersistThreads, 1)
 gemm_wt_persistent_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmX,
                           void* __restrict__ out, long long ldo, int T, int N, int kb_total, int tiles_t,
                           int total_tiles, int mode, int w_evict_first, const int* __restrict__ grp_tiles,
-                          const int* __restrict__ grp_seg, int grp_w_rows) {
+                          const int* __restrict__ grp_seg, int grp_w_rows, GateParams gate_params) {
     using Cfg = PersistCfg<TN>;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
@@ -508,7 +524,7 @@ gemm_wt_persistent_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_
                 waited = true;
             }
             const uint32_t tlane = tmem_base + acc * TN + (static_cast<uint32_t>(quarter * 32) << 16);
-            if (mode == ATX_GEMM_SWIGLU_BF16) {
+            if (is_glu(mode)) {
                 // symmetric exchange in groups of 32 token columns: gate warps finish columns [0, TN/2),
                 // up warps columns [TN/2, TN); each parks the half the other pair needs
                 constexpr int HALF = TN / 2;
@@ -542,7 +558,7 @@ gemm_wt_persistent_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_
                             const float gg = gate_warp ? mine : other, uu = gate_warp ? other : mine;
                             if (ok && t < t_end)
                                 o[static_cast<long long>(t) * ldo + col] =
-                                    __float2bfloat16_rn(gg / (1.f + expf(-gg)) * uu);
+                                    __float2bfloat16_rn(glu_value(gg, uu, mode, gate_params));
                         }
                     }
                     epi_bar_sync();  // the exchange buffer is reused by the next group
@@ -654,6 +670,7 @@ struct atx_gemm_plan {
     CUtensorMap tmX[5];  // one per token-tile size
     long long N, K, T_cap;
     int w_evict_first;
+    atx::GateParams gate;   // constants of ATX_GEMM_GLU_CLAMP_BF16
 };
 
 using namespace atx;
@@ -677,7 +694,7 @@ static int launch_gemm(const atx_gemm_plan* p, int ti, void* out, long long ldo,
     // the fused-SwiGLU epilogue parks half a tile in the stage buffers: keep them large enough
     // (a whole fp32 tile when the split-K cluster parks partial sums there)
     const bool ordered = (mode & 0x100) != 0;
-    if ((mode & 0xff) == ATX_GEMM_SWIGLU_BF16 || (mode & 0xff) == ATX_GEMM_ADD_F32 ||
+    if (is_glu(mode & 0xff) || (mode & 0xff) == ATX_GEMM_ADD_F32 ||
         ((mode & 0xff) == ATX_GEMM_RELU2_BF16 && zs > 1)) {
         // epilogues that park the tile in the (idle) stage buffers: half a tile for SwiGLU, a whole fp32 tile for the
         // split-K cluster reduction and for the 16-byte adds
@@ -699,7 +716,7 @@ static int launch_gemm(const atx_gemm_plan* p, int ti, void* out, long long ldo,
         attr[na].val.programmaticStreamSerializationAllowed = 1;
         ++na;
     }
-    if (((mode & 0xff) == ATX_GEMM_SWIGLU_BF16 || (mode & 0xff) == ATX_GEMM_RELU2_BF16 || ordered) && zs > 1) {  // the K-splits of one tile are one cluster (DSMEM reduction)
+    if ((is_glu(mode & 0xff) || (mode & 0xff) == ATX_GEMM_RELU2_BF16 || ordered) && zs > 1) {  // the K-splits of one tile are one cluster (DSMEM reduction)
         attr[na].id = cudaLaunchAttributeClusterDimension;
         attr[na].val.clusterDim.x = 1;
         attr[na].val.clusterDim.y = 1;
@@ -709,7 +726,7 @@ static int launch_gemm(const atx_gemm_plan* p, int ti, void* out, long long ldo,
     cfg.attrs = attr;
     cfg.numAttrs = na;
     ATX_CUDA(cudaLaunchKernelEx(&cfg, gemm_wt_kernel<TN>, p->tmW, p->tmX[ti], out, ldo, T,
-                                static_cast<int>(p->N), kb_total, kb_per, mode, p->w_evict_first, stages));
+                                static_cast<int>(p->N), kb_total, kb_per, mode, p->w_evict_first, stages, p->gate));
     return ATX_OK;
 }
 
@@ -741,7 +758,7 @@ static int launch_gemm_persistent(const atx_gemm_plan* p, int ti, void* out, lon
     cfg.numAttrs = pdl ? 1 : 0;
     ATX_CUDA(cudaLaunchKernelEx(&cfg, gemm_wt_persistent_kernel<TN>, p->tmW, p->tmX[ti], out, ldo, T,
                                 static_cast<int>(p->N), kb_total, tiles_t, total, mode, p->w_evict_first,
-                                static_cast<const int*>(nullptr), static_cast<const int*>(nullptr), 0));
+                                static_cast<const int*>(nullptr), static_cast<const int*>(nullptr), 0, p->gate));
     return ATX_OK;
 }
 
@@ -772,7 +789,7 @@ static int launch_gemm_grouped(const atx_gemm_plan* p, int ti, void* out, long l
     cfg.attrs = attr;
     cfg.numAttrs = pdl ? 1 : 0;
     ATX_CUDA(cudaLaunchKernelEx(&cfg, gemm_wt_persistent_kernel<TN>, p->tmW, p->tmX[ti], out, ldo, 0, n_group, kb_total, 1,
-                                0, mode, p->w_evict_first, tiles, seg, n_group));
+                                0, mode, p->w_evict_first, tiles, seg, n_group, p->gate));
     return ATX_OK;
 }
 
@@ -793,6 +810,7 @@ int atx_gemm_plan_create(atx_gemm_plan** plan, const void* W, long long N, long 
     p->T_cap = T_cap;
     // weights larger than L2 are streamed once per step: do not let them evict activations / KV
     p->w_evict_first = (N * K * 2 > (64ll << 20)) ? 1 : 0;
+    p->gate = atx::GateParams{1.f, 3.0e38f, 0.f};
     int rc = make_map(&p->tmW, W, N, K, K, kBM);
     for (int i = 0; i < 5 && rc == ATX_OK; ++i) rc = make_map(&p->tmX[i], X, T_cap, K, ldx, kTileSizes[i]);
     if (rc != ATX_OK) {
@@ -800,6 +818,12 @@ int atx_gemm_plan_create(atx_gemm_plan** plan, const void* W, long long N, long 
         return rc;
     }
     *plan = p;
+    return ATX_OK;
+}
+
+int atx_gemm_plan_set_gate(atx_gemm_plan* plan, float alpha, float limit, float shift) {
+    ATX_REQUIRE(plan && limit > 0.f, "atx_gemm_plan_set_gate: null plan or limit=%g", limit);
+    plan->gate = atx::GateParams{alpha, limit, shift};
     return ATX_OK;
 }
 
@@ -826,9 +850,9 @@ int atx_gemm_run(const atx_gemm_plan* p, void* out, long long ldo, int T, int mo
     cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
     ATX_REQUIRE(p && out, "atx_gemm_run: null pointer");
     ATX_REQUIRE(T > 0 && T <= p->T_cap, "atx_gemm_run: T=%d outside (0, %lld]", T, p->T_cap);
-    ATX_REQUIRE(mode >= ATX_GEMM_STORE_F32 && mode <= ATX_GEMM_RELU2_BF16, "atx_gemm_run: bad mode %d", mode);
-    ATX_REQUIRE(ldo >= (mode == ATX_GEMM_SWIGLU_BF16 ? p->N / 2 : p->N), "atx_gemm_run: ldo=%lld too small for N=%lld", ldo, p->N);
-    ATX_REQUIRE(mode != ATX_GEMM_SWIGLU_BF16 || p->N % 128 == 0, "atx_gemm_run: SWIGLU mode needs N %% 128 == 0");
+    ATX_REQUIRE(mode >= ATX_GEMM_STORE_F32 && mode <= ATX_GEMM_GLU_CLAMP_BF16, "atx_gemm_run: bad mode %d", mode);
+    ATX_REQUIRE(ldo >= (is_glu(mode) ? p->N / 2 : p->N), "atx_gemm_run: ldo=%lld too small for N=%lld", ldo, p->N);
+    ATX_REQUIRE(!is_glu(mode) || p->N % 128 == 0, "atx_gemm_run: SWIGLU mode needs N %% 128 == 0");
     // ATX_FLAG_ORDERED: the K-splits of an ADD are reduced inside a cluster in a fixed order (as for SwiGLU) and ONE CTA
     // adds each output element, instead of every split racing its red.add: bit-reproducible, a little slower
     const bool ordered = (flags & ATX_FLAG_ORDERED) && mode == ATX_GEMM_ADD_F32 && T <= 64;
@@ -840,12 +864,12 @@ int atx_gemm_run(const atx_gemm_plan* p, void* out, long long ldo, int T, int mo
     if (splits <= 0) {
         splits = 1;
         if (mode == ATX_GEMM_ADD_F32) splits = atx_gemm_auto_splits(p->N, p->K, T);
-        if ((mode == ATX_GEMM_SWIGLU_BF16 || mode == ATX_GEMM_RELU2_BF16) && T <= 64) {  // cluster split-K: a power of two, at most 8 CTAs
+        if ((is_glu(mode) || mode == ATX_GEMM_RELU2_BF16) && T <= 64) {  // cluster split-K: a power of two, at most 8 CTAs
             const int want = atx_gemm_auto_splits(p->N, p->K, T);
             while (splits * 2 <= want && splits * 2 <= 8 && (p->K / kBK) % (splits * 2) == 0) splits *= 2;
         }
     }
-    const bool act_mode = mode == ATX_GEMM_SWIGLU_BF16 || mode == ATX_GEMM_RELU2_BF16;
+    const bool act_mode = is_glu(mode) || mode == ATX_GEMM_RELU2_BF16;
     ATX_REQUIRE(splits == 1 || mode == ATX_GEMM_ADD_F32 || act_mode,
                 "atx_gemm_run: split-K (%d) needs ATX_GEMM_ADD_F32 into a zeroed or residual buffer, or "
                 "ATX_GEMM_SWIGLU_BF16 / ATX_GEMM_RELU2_BF16 (cluster reduction)", splits);
@@ -871,11 +895,11 @@ int atx_gemm_run_grouped(const atx_gemm_plan* p, void* out, long long ldo, int n
     ATX_REQUIRE(p && out && seg_off && tiles, "atx_gemm_run_grouped: null pointer");
     ATX_REQUIRE(n_group > 0 && p->N % n_group == 0 && max_row_tiles > 0,
                 "atx_gemm_run_grouped: W has %lld rows, not a multiple of %d per group", p->N, n_group);
-    ATX_REQUIRE(mode == ATX_GEMM_STORE_F32 || mode == ATX_GEMM_SWIGLU_BF16 || mode == ATX_GEMM_STORE_BF16 ||
+    ATX_REQUIRE(mode == ATX_GEMM_STORE_F32 || is_glu(mode) || mode == ATX_GEMM_STORE_BF16 ||
                     mode == ATX_GEMM_RELU2_BF16,
                 "atx_gemm_run_grouped: mode %d (stores only: the rows of a group are written once)", mode);
-    ATX_REQUIRE(ldo >= (mode == ATX_GEMM_SWIGLU_BF16 ? n_group / 2 : n_group), "atx_gemm_run_grouped: ldo=%lld too small", ldo);
-    ATX_REQUIRE(mode != ATX_GEMM_SWIGLU_BF16 || n_group % 128 == 0, "atx_gemm_run_grouped: SWIGLU mode needs %d %% 128 == 0",
+    ATX_REQUIRE(ldo >= (is_glu(mode) ? n_group / 2 : n_group), "atx_gemm_run_grouped: ldo=%lld too small", ldo);
+    ATX_REQUIRE(!is_glu(mode) || n_group % 128 == 0, "atx_gemm_run_grouped: SWIGLU mode needs %d %% 128 == 0",
                 n_group);
     return launch_gemm_grouped<256>(p, 4, out, ldo, n_group, mode, seg_off, tiles, max_row_tiles, (flags & ATX_FLAG_PDL) ? 1 : 0,
                                     reinterpret_cast<cudaStream_t>(stream_));

@@ -524,7 +524,7 @@ conv_state_update_kernel(const float* __restrict__ in, long long ld, int x_off, 
 // what a mixer reads is its input plus a causal convolution of it. x is the fp32 stream [T, ld]; rows before the step come
 // from conv_state [slots, K-1, C] (atx_conv_state_update keeps it), rows before position 0 are zero. A CTA takes kConvRows
 // consecutive rows x 256 channels; a thread walks its channel down the rows, so an input is fetched from memory once.
-template <typename XT>
+template <typename XT, int NV>   // NV = 4: four channels per thread with 16-byte accesses (sizes, pitches and pointers allow it)
 __global__ void __launch_bounds__(256)
 conv_residual_kernel(const float* __restrict__ x, long long ld, const XT* __restrict__ w, const float* __restrict__ conv_state,
                      XT* __restrict__ out, long long ldo, const int* __restrict__ tok_seq, const int* __restrict__ seq_start,
@@ -532,34 +532,75 @@ conv_residual_kernel(const float* __restrict__ x, long long ld, const XT* __rest
     pdl_launch_dependents();
     pdl_wait();
     const int t0 = blockIdx.x * rows_per;
-    const int c = blockIdx.y * blockDim.x + threadIdx.x;
+    const int c = (blockIdx.y * blockDim.x + threadIdx.x) * NV;
     if (c >= C) return;
-    float wt[kConvMaxTaps];
+    float wt[kConvMaxTaps][NV], win[kConvMaxTaps - 1][NV];
 #pragma unroll
-    for (int j = 0; j < kConvMaxTaps; ++j) wt[j] = j < K ? ldf(w, static_cast<long long>(c) * K + j) : 0.f;
+    for (int j = 0; j < kConvMaxTaps; ++j)
+#pragma unroll
+        for (int e = 0; e < NV; ++e) wt[j][e] = j < K ? ldf(w, static_cast<long long>(c + e) * K + j) : 0.f;
+    auto load = [&](const float* p, float (&v)[NV]) {
+        if (NV == 4) {
+            const float4 f = *reinterpret_cast<const float4*>(p);
+            v[0] = f.x, v[NV > 1 ? 1 : 0] = f.y, v[NV > 2 ? 2 : 0] = f.z, v[NV > 3 ? 3 : 0] = f.w;
+        } else {
+            v[0] = *p;
+        }
+    };
+    int prev_s = -1, prev_i = -2;
     for (int r = 0; r < rows_per && t0 + r < T; ++r) {
         const long long t = t0 + r;
         const int s = tok_seq[t];
         if (s < 0) continue;
         const int i = static_cast<int>(t) - seq_start[s];
-        const int pos0 = seq_pos0[s];
-        const float* st = conv_state + static_cast<long long>(seq_slot[s]) * (K - 1) * C;
-        const float cur = x[t * ld + c];
-        float acc = cur;
+        if (s != prev_s || i != prev_i + 1) {   // the window of the K-1 rows before this one: earlier rows of the portion, or the slot
+            const int pos0 = seq_pos0[s];
+            const float* st = conv_state + static_cast<long long>(seq_slot[s]) * (K - 1) * C;
 #pragma unroll
-        for (int j = 0; j < kConvMaxTaps; ++j) {
-            if (j >= K) break;
-            const int rel = i - (K - 1 - j);
-            float v = 0.f;
-            if (j == K - 1)
-                v = cur;
-            else if (rel >= 0)
-                v = x[(t - i + rel) * ld + c];   // an earlier row of the same portion (L1 / L2: the rows above in this tile)
-            else if (pos0 + rel >= 0)
-                v = st[static_cast<long long>(K - 1 + rel) * C + c];
-            acc = fmaf(wt[j], v, acc);
+            for (int j = 0; j < kConvMaxTaps - 1; ++j) {
+#pragma unroll
+                for (int e = 0; e < NV; ++e) win[j][e] = 0.f;
+                if (j < K - 1) {
+                    const int rel = i - (K - 1) + j;
+                    if (rel >= 0)
+                        load(x + (t - i + rel) * ld + c, win[j]);
+                    else if (pos0 + rel >= 0)
+                        load(st + static_cast<long long>(K - 1 + rel) * C + c, win[j]);
+                }
+            }
         }
-        stf(out + t * ldo, c, acc);
+        float cur[NV], acc[NV];
+        load(x + t * ld + c, cur);
+#pragma unroll
+        for (int e = 0; e < NV; ++e) acc[e] = cur[e];
+#pragma unroll
+        for (int j = 0; j < kConvMaxTaps - 1; ++j)
+            if (j < K - 1)
+#pragma unroll
+                for (int e = 0; e < NV; ++e) acc[e] = fmaf(wt[j][e], win[j][e], acc[e]);
+#pragma unroll
+        for (int j = 0; j < kConvMaxTaps; ++j)
+            if (j == K - 1)
+#pragma unroll
+                for (int e = 0; e < NV; ++e) acc[e] = fmaf(wt[j][e], cur[e], acc[e]);
+        if (NV == 4) {
+            st4(out + t * ldo + c, 0, make_float4(acc[0], acc[NV > 1 ? 1 : 0], acc[NV > 2 ? 2 : 0], acc[NV > 3 ? 3 : 0]));
+        } else {
+            stf(out + t * ldo, c, acc[0]);
+        }
+        // slide: entries 0 .. K-2 hold the K-1 inputs before the next row
+#pragma unroll
+        for (int j = 0; j < kConvMaxTaps - 2; ++j)
+            if (j < K - 2)
+#pragma unroll
+                for (int e = 0; e < NV; ++e) win[j][e] = win[j + 1][e];
+#pragma unroll
+        for (int j = 0; j < kConvMaxTaps - 1; ++j)
+            if (j == K - 2)
+#pragma unroll
+                for (int e = 0; e < NV; ++e) win[j][e] = cur[e];
+        prev_s = s;
+        prev_i = i;
     }
 }
 
@@ -930,7 +971,9 @@ int atx_gated_norm_groups(const float* y, long long ldy, const float* gate, long
     cudaLaunchConfig_t cfg = {};
     cudaLaunchAttribute attr[1];
     cfg.gridDim = dim3(T, groups);
-    cfg.blockDim = dim3(T <= 512 && n / groups >= 2048 ? 1024 : 256);
+    // a thread takes four elements at a time: narrow groups (a norm per head) get a CTA of as many warps as that needs
+    const int lanes = (n / groups + 3) / 4;
+    cfg.blockDim = dim3(T <= 512 && n / groups >= 2048 ? 1024 : lanes <= 32 ? 32 : lanes <= 64 ? 64 : lanes <= 128 ? 128 : 256);
     cfg.stream = reinterpret_cast<cudaStream_t>(stream);
     set_pdl2(cfg, attr, flags);
     auto al16 = [](const void* p) { return reinterpret_cast<uintptr_t>(p) % 16 == 0; };
@@ -1070,16 +1113,26 @@ int atx_conv_residual(const float* x, long long ld, const void* w, const float* 
                 "atx_conv_residual: null pointer");
     ATX_REQUIRE(T > 0 && C > 0 && K >= 1 && K <= kConvMaxTaps, "atx_conv_residual: bad shape T=%d C=%d taps=%d (<= %d)", T, C,
                 K, kConvMaxTaps);
-    const int rows_per = T >= 256 ? kConvRows : 1;   // few rows (decode): a CTA per row and 256 channels
+    const int rows_per = T >= 256 ? kConvRows : 1;   // few rows (decode): a CTA per row
+    auto al16 = [](const void* p) { return reinterpret_cast<uintptr_t>(p) % 16 == 0; };
+    const bool v4 = C % 4 == 0 && ld % 4 == 0 && ldo % 4 == 0 && al16(x) && al16(out) && (K == 1 || al16(conv_state));
+    const int per_cta = v4 ? 128 * 4 : 256;          // channels a CTA covers
     cudaLaunchConfig_t cfg = {};
     cudaLaunchAttribute attr[1];
-    cfg.gridDim = dim3((T + rows_per - 1) / rows_per, (C + 255) / 256);
-    cfg.blockDim = dim3(256);
+    cfg.gridDim = dim3((T + rows_per - 1) / rows_per, (C + per_cta - 1) / per_cta);
+    cfg.blockDim = dim3(v4 ? 128 : 256);
     cfg.stream = reinterpret_cast<cudaStream_t>(stream);
     set_pdl2(cfg, attr, flags);
-    ATX_DISPATCH_XT(dtype, ATX_CUDA(cudaLaunchKernelEx(&cfg, conv_residual_kernel<XT>, x, ld, reinterpret_cast<const XT*>(w),
-                                                       conv_state, reinterpret_cast<XT*>(out), ldo, tok_seq, seq_start,
-                                                       seq_pos0, seq_slot, T, C, K, rows_per)));
+#define ATX_CONV_RES(NV_)                                                                                                  \
+    ATX_DISPATCH_XT(dtype, ATX_CUDA(cudaLaunchKernelEx(&cfg, conv_residual_kernel<XT, NV_>, x, ld,                         \
+                                                       reinterpret_cast<const XT*>(w), conv_state,                         \
+                                                       reinterpret_cast<XT*>(out), ldo, tok_seq, seq_start, seq_pos0,      \
+                                                       seq_slot, T, C, K, rows_per)))
+    if (v4)
+        ATX_CONV_RES(4);
+    else
+        ATX_CONV_RES(1);
+#undef ATX_CONV_RES
     return ATX_OK;
 }
 

@@ -515,7 +515,9 @@ def routed_trace_measure(world: int, device_ecfg, model: str = "random:8b:0") ->
 
 # ------------------------------------------------------------------------------------------------------
 def safisun_measure(args, local, pk, family: str = "safisun") -> dict:
-    """`--workload safisun | gopopel | zonidra`: prefill and decode throughput of a layer-list family (Zonidra: sigmoid
+    """`--workload safisun | gopopel | zonidra | napuzen`: prefill and decode throughput of a layer-list family (Napuzen:
+    per-channel decayed linear attention, latent attention with and without positions, residual convolutions, clamped and
+    expert feed-forwards, beside the Zonidra, the Safisun and the Llama shape; Zonidra: sigmoid
     attention under a window with kept first keys, token shift, dense and expert feed-forwards, beside the Gopopel and the
     Llama shape; Safisun: state-space,
     linear-attention and block-local attention mixers; Gopopel: parallel layers of latent attention and windowed
@@ -535,7 +537,8 @@ def safisun_measure(args, local, pk, family: str = "safisun") -> dict:
     B, P, O = args.arch_batch, args.arch_prompt, args.arch_out
     records, launches = [], 0
     for size in [x for x in args.arch_sizes.split(",") if x]:
-        beside = {"safisun": (), "gopopel": (f"random:safisun-{size}:0",), "zonidra": (f"random:gopopel-{size}:0",)}[family]
+        beside = {"safisun": (), "gopopel": (f"random:safisun-{size}:0",), "zonidra": (f"random:gopopel-{size}:0",),
+                  "napuzen": (f"random:zonidra-{size}:0", f"random:safisun-{size}:0")}[family]
         for model in (f"random:{family}-{size}:0",) + beside + (f"random:{size}:0",):
             src = resolve_model(model)
             ecfg = EngineConfig(max_model_len=P + O + 16, max_num_seqs=B, max_num_batched_tokens=8192,
@@ -709,7 +712,7 @@ def run_other_workload(args, rank, world, local):
                     "config": {"workload": f"BASELINE configs[4]: Llama-3.1-8B long-context, batch {B} x {P}-token prompts "
                                            f"(chunked prefill, 8192-token budget) + {O} greedy tokens over paged KV",
                                "parallelism": "1 GPU", "kv_blocks": r.num_blocks}})
-    elif args.workload in ("safisun", "gopopel", "zonidra"):
+    elif args.workload in ("safisun", "gopopel", "zonidra", "napuzen"):
         out.update(safisun_measure(args, local, pk, args.workload))
         if rank == 0:
             print(json.dumps(out), flush=True)
@@ -744,12 +747,12 @@ def main() -> None:
     ap.add_argument("--no-multi", action="store_true", help="N > 1: skip the routed-DP and 70B-TP records")
     ap.add_argument("--tp70b-any-n", action="store_true", help="attach the 70B tensor-parallel record at any N > 1 "
                                                                "(default: only at N = 8, BASELINE configs[3])")
-    ap.add_argument("--arch-sizes", default="1b,8b", help="--workload safisun | gopopel | zonidra: shapes to run (each beside the Llama shape "
+    ap.add_argument("--arch-sizes", default="1b,8b", help="--workload safisun | gopopel | zonidra | napuzen: shapes to run (each beside the Llama shape "
                                                           "of the same width, depth, feed-forward and vocabulary)")
     ap.add_argument("--arch-batch", type=int, default=8)
     ap.add_argument("--arch-prompt", type=int, default=2048)
     ap.add_argument("--arch-out", type=int, default=64)
-    ap.add_argument("--workload", default="fanout", choices=["fanout", "trace", "long", "tp70b", "safisun", "gopopel", "zonidra"],
+    ap.add_argument("--workload", default="fanout", choices=["fanout", "trace", "long", "tp70b", "safisun", "gopopel", "zonidra", "napuzen"],
                     help="fanout = headline BASELINE configs[1] (default); the others are configs[2..4]")
     ap.add_argument("--trace-out", default="", help="directory for response.json / llm_calls.jsonl of a trace replay")
     ap.add_argument("--long-out", type=int, default=128)

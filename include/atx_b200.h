@@ -63,9 +63,13 @@ typedef struct atx_gemm_plan atx_gemm_plan;
 /* out bf16 = max(acc, 0)^2: the activation between the GEMMs of a feed-forward without a gate. Split-K (T <= 64) as for
  * SwiGLU: the splits of a tile are one cluster, summed in a fixed order before the activation. */
 #define ATX_GEMM_RELU2_BF16 4
+/* ATX_GEMM_SWIGLU_BF16 with clamps (same row layout, same split-K): out = g sigmoid(alpha g) (u + shift) with g = min(acc_gate,
+ * limit), u = clamp(acc_up, -limit, limit); the constants are the plan's (atx_gemm_plan_set_gate). */
+#define ATX_GEMM_GLU_CLAMP_BF16 5
 int atx_gemm_plan_create(atx_gemm_plan** plan, const void* W, long long N, long long K, const void* X,
                          long long T_cap, long long ldx);
 void atx_gemm_plan_destroy(atx_gemm_plan* plan);
+int atx_gemm_plan_set_gate(atx_gemm_plan* plan, float alpha, float limit, float shift);
 /* splits: K partitions (>=1); 0 = choose (ADD and SWIGLU modes may split). ldo: out row pitch in elements. */
 int atx_gemm_run(const atx_gemm_plan* plan, void* out, long long ldo, int T, int mode, int splits,
                  int flags, atx_stream_t stream);

@@ -739,3 +739,31 @@ def test_clamped_gate_norm_per_head_plain_stream_rows_and_renormalised_routing(d
     val, idx = s.topk(4, -1)
     assert torch.equal(sel.cpu().long(), idx)
     assert float((wgt.double().cpu() - val / val.sum(-1, keepdim=True) * 2.5).abs().max()) < 1e-6
+
+
+@pytest.mark.parametrize("T,F,K", [(5, 128, 512), (64, 192, 1024), (100, 384, 128), (300, 512, 320)])
+def test_gemm_with_the_clamped_gate_in_its_epilogue(T, F, K):
+    """Gate and up rows in blocks of 64; decode-sized steps cut K over a cluster and sum the parts before the clamps;
+    prompt-sized steps take the persistent kernel. The plain gated mode of the same plan keeps its own formula."""
+    from atx.weights import interleave_gate_up
+
+    L, Cb = lib()
+    g = torch.Generator().manual_seed(T + F)
+    gate, up = ((3.0 * torch.randn(F, K, generator=g) / K ** 0.5).to(torch.bfloat16) for _ in range(2))
+    w = interleave_gate_up(gate, up).contiguous().to(DEV)
+    x = torch.zeros(max(T, 16), K, dtype=torch.bfloat16, device=DEV)
+    x[:T] = torch.randn(T, K, generator=g).to(torch.bfloat16).to(DEV)
+    plan = Cb.GemmPlan(w, x)
+    plan.set_gate(1.702, 1.25, 1.0)
+    out = torch.full((T, F + 8), 3.0, dtype=torch.bfloat16, device=DEV)
+    plan.run(out, T, Cb.GEMM_GLU_CLAMP_BF16)
+    torch.cuda.synchronize()
+    xg, xu = x[:T].cpu().double() @ gate.double().T, x[:T].cpu().double() @ up.double().T
+    gg, uu = xg.clamp(max=1.25), xu.clamp(-1.25, 1.25)
+    want = gg * torch.sigmoid(1.702 * gg) * (uu + 1.0)
+    assert float((xg > 1.25).double().mean()) > 0.05 and float((xu < -1.25).double().mean()) > 0.05      # the clamps bite
+    assert torch.allclose(out[:, :F].cpu().double(), want, atol=2e-2, rtol=1e-2)
+    assert float((out[:, F:].float() - 3.0).abs().max()) == 0.0
+    plan.run(out, T, Cb.GEMM_SWIGLU_BF16)
+    torch.cuda.synchronize()
+    assert torch.allclose(out[:, :F].cpu().double(), xg * torch.sigmoid(xg) * xu, atol=3e-2, rtol=1e-2)
