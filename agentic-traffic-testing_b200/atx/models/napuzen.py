@@ -89,8 +89,8 @@ class Config:
         return cfg
 
     def validate(self) -> None:
-        if not 0 <= self.taps <= 8:
-            raise ValueError(f"canon.taps={self.taps}: the convolution kernel holds at most 8 taps")
+        if self.taps < 0:
+            raise ValueError(f"canon.taps={self.taps} must not be negative")
         for i, l in enumerate(self.layers):
             if l["type"] not in MIXERS:
                 raise ValueError(f"layer {i}: unknown mixer type {l['type']!r}")

@@ -360,6 +360,39 @@ gated_norm_kernel(const float* __restrict__ y, long long ldy, const float* __res
     }
 }
 
+// The same for narrow groups (a norm per head): a CTA per row, a warp per group and a lane per four elements, so that a row
+// of many heads is one CTA instead of one small CTA per head. n_group a multiple of 4, at most 128; pointers and pitches as
+// for the four-element path above.
+template <typename XT>
+__global__ void __launch_bounds__(256)
+gated_norm_warp_kernel(const float* __restrict__ y, long long ldy, const float* __restrict__ gate, long long ldg,
+                       const XT* __restrict__ w, XT* __restrict__ out, long long ldo, int n_group, int groups, float eps,
+                       int mode, float scale, int w_shared) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const long long t = blockIdx.x;
+    const int lane = threadIdx.x & 31, n4 = n_group / 4;
+    const bool on = lane < n4;
+    for (int gidx = threadIdx.x >> 5; gidx < groups; gidx += blockDim.x >> 5) {
+        const int c0 = gidx * n_group;
+        float4 v = make_float4(0.f, 0.f, 0.f, 0.f), g = v;
+        if (on) {
+            v = ld4(y + t * ldy + c0, lane);
+            g = ld4(gate + t * ldg + c0, lane);
+            if (mode == 1) v.x *= silu_f(g.x), v.y *= silu_f(g.y), v.z *= silu_f(g.z), v.w *= silu_f(g.w);
+        }
+        const float rs = rsqrtf(warp_sum(v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w) / static_cast<float>(n_group) + eps) * scale;
+        if (!on) continue;
+        const float4 ww = ld4(w_shared ? w : w + c0, lane);
+        v.x *= rs * ww.x, v.y *= rs * ww.y, v.z *= rs * ww.z, v.w *= rs * ww.w;
+        if (mode == 0)
+            v.x *= sigmoid_f(g.x), v.y *= sigmoid_f(g.y), v.z *= sigmoid_f(g.z), v.w *= sigmoid_f(g.w);
+        else if (mode == 2)
+            v.x *= silu_f(g.x), v.y *= silu_f(g.y), v.z *= silu_f(g.z), v.w *= silu_f(g.w);
+        st4(out + t * ldo + c0, lane, v);
+    }
+}
+
 // ---- short causal convolution + silu, step size and decay of the selective scan -------------------------------------
 // Channel c of row t: out = silu(b[c] + sum_j w[c][j] * in[row(t) - (K-1-j)]), the last tap being the row itself. Inputs
 // before the step's first row come from the carried window conv_state[slot][K-1][C] (raw inputs of the last K-1
@@ -601,6 +634,35 @@ conv_residual_kernel(const float* __restrict__ x, long long ld, const XT* __rest
                 for (int e = 0; e < NV; ++e) win[j][e] = cur[e];
         prev_s = s;
         prev_i = i;
+    }
+}
+
+// More taps than the register window holds: a thread per (row, channel) sums its taps straight from memory.
+template <typename XT>
+__global__ void __launch_bounds__(256)
+conv_residual_long_kernel(const float* __restrict__ x, long long ld, const XT* __restrict__ w,
+                          const float* __restrict__ conv_state, XT* __restrict__ out, long long ldo,
+                          const int* __restrict__ tok_seq, const int* __restrict__ seq_start,
+                          const int* __restrict__ seq_pos0, const int* __restrict__ seq_slot, int C, int K) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const long long t = blockIdx.x;
+    const int s = tok_seq[t];
+    if (s < 0) return;
+    const int i = static_cast<int>(t) - seq_start[s], pos0 = seq_pos0[s];
+    const float* st = conv_state + static_cast<long long>(seq_slot[s]) * (K - 1) * C;
+    for (int c = blockIdx.y * blockDim.x + threadIdx.x; c < C; c += gridDim.y * blockDim.x) {
+        float acc = x[t * ld + c];
+        for (int j = 0; j < K; ++j) {
+            const int rel = i - (K - 1 - j);
+            float v = 0.f;
+            if (rel >= 0)
+                v = x[(t - i + rel) * ld + c];
+            else if (pos0 + rel >= 0)
+                v = st[static_cast<long long>(K - 1 + rel) * C + c];
+            acc = fmaf(ldf(w, static_cast<long long>(c) * K + j), v, acc);
+        }
+        stf(out + t * ldo, c, acc);
     }
 }
 
@@ -984,6 +1046,14 @@ int atx_gated_norm_groups(const float* y, long long ldy, const float* gate, long
     ATX_DISPATCH_XT(dtype, ATX_CUDA(cudaLaunchKernelEx(&cfg, gated_norm_kernel<XT, VEC_>, y, ldy, gate, ldg,             \
                                                        reinterpret_cast<const XT*>(w), reinterpret_cast<XT*>(out), ldo,  \
                                                        ng, eps, mode, scale, w_shared)))
+    if (v4 && ng <= 128 && groups > 1) {
+        cfg.gridDim = dim3(T);
+        cfg.blockDim = dim3(groups >= 8 ? 256 : 32 * groups);
+        ATX_DISPATCH_XT(dtype, ATX_CUDA(cudaLaunchKernelEx(&cfg, gated_norm_warp_kernel<XT>, y, ldy, gate, ldg,
+                                                           reinterpret_cast<const XT*>(w), reinterpret_cast<XT*>(out), ldo,
+                                                           ng, groups, eps, mode, scale, w_shared)));
+        return ATX_OK;
+    }
     if (v4) {
         cfg.dynamicSmemBytes = static_cast<size_t>(ng) * 4;
         if (ng * 4 > 48 * 1024) {
@@ -1111,8 +1181,20 @@ int atx_conv_residual(const float* x, long long ld, const void* w, const float* 
                       int K, int dtype, int flags, atx_stream_t stream) {
     ATX_REQUIRE(x && w && out && tok_seq && seq_start && seq_pos0 && seq_slot && (K == 1 || conv_state),
                 "atx_conv_residual: null pointer");
-    ATX_REQUIRE(T > 0 && C > 0 && K >= 1 && K <= kConvMaxTaps, "atx_conv_residual: bad shape T=%d C=%d taps=%d (<= %d)", T, C,
-                K, kConvMaxTaps);
+    ATX_REQUIRE(T > 0 && C > 0 && K >= 1, "atx_conv_residual: bad shape T=%d C=%d taps=%d", T, C, K);
+    if (K > kConvMaxTaps) {
+        cudaLaunchConfig_t lc = {};
+        cudaLaunchAttribute la[1];
+        lc.gridDim = dim3(T, (C + 255) / 256);
+        lc.blockDim = dim3(256);
+        lc.stream = reinterpret_cast<cudaStream_t>(stream);
+        set_pdl2(lc, la, flags);
+        ATX_DISPATCH_XT(dtype, ATX_CUDA(cudaLaunchKernelEx(&lc, conv_residual_long_kernel<XT>, x, ld,
+                                                           reinterpret_cast<const XT*>(w), conv_state,
+                                                           reinterpret_cast<XT*>(out), ldo, tok_seq, seq_start, seq_pos0,
+                                                           seq_slot, C, K)));
+        return ATX_OK;
+    }
     const int rows_per = T >= 256 ? kConvRows : 1;   // few rows (decode): a CTA per row
     auto al16 = [](const void* p) { return reinterpret_cast<uintptr_t>(p) % 16 == 0; };
     const bool v4 = C % 4 == 0 && ld % 4 == 0 && ldo % 4 == 0 && al16(x) && al16(out) && (K == 1 || al16(conv_state));

@@ -509,7 +509,7 @@ int atx_gated_act_clamped(const float* gu, void* out, int T, int I, float alpha,
 int atx_gated_norm_groups(const float* y, long long ldy, const float* gate, long long ldg, const void* w, int w_shared,
                           void* out, long long ldo, int T, int n, int groups, float eps, int mode, float scale, int dtype,
                           int flags, atx_stream_t stream);
-/* out[t, c] = x[t, c] + sum_j w[c, j] * x[t - (K - 1 - j), c] over the rows of t's sequence (K taps, at most 8; w [C, K] of
+/* out[t, c] = x[t, c] + sum_j w[c, j] * x[t - (K - 1 - j), c] over the rows of t's sequence (K taps; w [C, K] of
  * the element type; no bias, no activation): x fp32 [T, ld], out of the element type [T, ldo]. The K - 1 rows before a
  * step come from conv_state [slots, K - 1, C] fp32, which atx_conv_state_update(x, ld, 0, ...) refreshes after this call;
  * rows before position 0 are zero. Rows with tok_seq < 0 are skipped. */

@@ -190,7 +190,7 @@ def test_one_layer_models(kind, width, dtype):
     eng.runner.close()
 
 
-@pytest.mark.parametrize("taps", [0, 1, 2, 3, 8])
+@pytest.mark.parametrize("taps", [0, 1, 2, 3, 8, 11])
 def test_convolution_lengths(taps):
     cfg = model_cfg([gla(mlp=dense()), lat2()], taps=taps)
     wt = R.random_checkpoint(cfg, 4)
@@ -587,7 +587,7 @@ def seq_view(counts, pos0, slots):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("K,C,T", [(3, 40, 50), (4, 300, 700), (2, 7, 3), (8, 64, 300), (1, 16, 20)])
+@pytest.mark.parametrize("K,C,T", [(3, 40, 50), (4, 300, 700), (2, 7, 3), (8, 64, 300), (1, 16, 20), (13, 24, 300)])
 def test_residual_convolution_carries_its_rows_across_steps_and_slots(K, C, T, dtype):
     L, Cb = lib()
     xt = torch.float32 if dtype == "float32" else torch.bfloat16

@@ -50,7 +50,7 @@ def test_config_is_read_from_json_and_picked_by_architecture(tmp_path):
                         (("layers", 3, "mixer", "kv_from"), 2), (("layers", 3, "mixer", "kv_rank"), 16),
                         (("layers", 2, "mixer", "rot", "dims"), 6), (("layers", 1, "mlp", "router", "top"), 6),
                         (("layers", 0, "mlp", "kind"), "glu"), (("layers", 0, "mixer", "tau"), 0.0),
-                        (("layers", 0, "mlp", "limit"), 0.0), (("canon", "taps"), 9)):
+                        (("layers", 0, "mlp", "limit"), 0.0), (("canon", "taps"), -1)):
         bad = json.loads(json.dumps(cfg))
         d = bad
         for k in path[:-1]:
