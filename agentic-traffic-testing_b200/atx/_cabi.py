@@ -49,6 +49,7 @@ EXPORTS = [
     "atx_gemm_run_grouped", "atx_gemm_grouped_tile_rows",
     "atx_resid_norm_out", "atx_gated_act_clamped", "atx_gated_norm_groups", "atx_conv_residual", "atx_lowrank_logdecay",
     "atx_gated_linear_recurrence", "atx_moe_route_opts", "atx_gemm_plan_set_gate",
+    "atx_gated_linear_recurrence_chunked", "atx_gated_linear_recurrence_chunked_supported",
 ]
 ATTN_SOFTMAX = 0
 ATTN_SIGMOID = 1
@@ -203,6 +204,8 @@ def load() -> C.CDLL:
     lib.atx_gated_linear_recurrence.argtypes = [vp, i64, vp, i64, vp, i64, vp, i64, i32, i32, i32, f32, vp, vp, i64, vp, vp,
                                                 vp, vp, i32, i32, vp]
     lib.atx_gemm_plan_set_gate.argtypes = [vp, f32, f32, f32]
+    lib.atx_gated_linear_recurrence_chunked.argtypes = list(lib.atx_gated_linear_recurrence.argtypes)
+    lib.atx_gated_linear_recurrence_chunked_supported.argtypes = [i32]
     lib.atx_moe_route_opts.argtypes = [vp, i64, vp, i32, i32, f32, i32, vp, vp, i32, i32, vp]
     for name in EXPORTS:  # fail at load time, not at first use, if the build is stale
         getattr(lib, name)

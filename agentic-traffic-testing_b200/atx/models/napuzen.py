@@ -696,9 +696,17 @@ class Program:
                 ldec, rec = self.ldec.data_ptr(), self.rec.data_ptr()
                 ck(lib.atx_lowrank_logdecay(proj + 4 * o_a, ld, l.a2.data_ptr(), l.a2_b.data_ptr(), ldec, H * D, T, H * D, rk,
                                             float(c["tau"]), dt, fl, st))
-                ck(lib.atx_gated_linear_recurrence(proj, ld, proj + 4 * o_k, ld, proj + 4 * o_v, ld, ldec, H * D, H, D, Vd,
-                                                   float(D) ** -0.5, self.state[li].data_ptr(), rec, H * Vd, *seqs4, n_seqs,
-                                                   fl, st))
+                # single decoded tokens (the first n_dec sequences) token by token on the FMA pipe; prompt portions in chunks
+                # on the tensor cores when the elements are bf16 and the kernel has the key size, else token by token as well
+                chunked = n_pf > 0 and dt == _cabi.DT_BF16 and lib.atx_gated_linear_recurrence_chunked_supported(D)
+                n_tok = n_dec if chunked else n_seqs
+                rargs = (proj, ld, proj + 4 * o_k, ld, proj + 4 * o_v, ld, ldec, H * D, H, D, Vd, float(D) ** -0.5,
+                         self.state[li].data_ptr(), rec, H * Vd)
+                if n_tok:
+                    ck(lib.atx_gated_linear_recurrence(*rargs, *seqs4, n_tok, fl, st))
+                if chunked:
+                    ck(lib.atx_gated_linear_recurrence_chunked(*rargs, *(p + 4 * n_dec for p in seqs4), n_pf, fl, st))
+                    n += 1 if n_tok else 0
                 ck(lib.atx_gated_norm_groups(rec, H * Vd, proj + 4 * o_g, ld, l.mix_norm.data_ptr(), 1, mix, K_o, T, H * Vd, H,
                                              eps, 2, 1.0, dt, fl, st))
                 n += 3

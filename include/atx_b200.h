@@ -526,6 +526,16 @@ int atx_gated_linear_recurrence(const float* q, long long ldq, const float* k, l
                                 const float* ldecay, long long ldc, int H, int D, int V, float qscale, float* state,
                                 float* y, long long ldy, const int* seq_start, const int* seq_count, const int* seq_pos0,
                                 const int* seq_slot, int n_seqs, int flags, atx_stream_t stream);
+/* The same recurrence for prompt portions in a chunk-parallel form on the tensor cores (chunks of 16 tokens: state read-out,
+ * pair weights times values and the state update are bf16 MMAs with fp32 accumulation; the pair weights inside a chunk, the
+ * state, the logarithms, their running sums and every exponential stay fp32). Same arguments and state layout, so a
+ * sequence may switch between the two from step to step. D must be one of the sizes ..._supported() accepts. */
+int atx_gated_linear_recurrence_chunked_supported(int D);
+int atx_gated_linear_recurrence_chunked(const float* q, long long ldq, const float* k, long long ldk, const float* v,
+                                        long long ldv, const float* ldecay, long long ldc, int H, int D, int V, float qscale,
+                                        float* state, float* y, long long ldy, const int* seq_start, const int* seq_count,
+                                        const int* seq_pos0, const int* seq_slot, int n_seqs, int flags,
+                                        atx_stream_t stream);
 /* atx_moe_route with normalize != 0: wgt = score / (sum of the chosen scores + 1e-20) * scale. */
 int atx_moe_route_opts(const float* logits, long long ld, const float* correction, int R, int top, float scale,
                        int normalize, int* sel, float* wgt, int T, int flags, atx_stream_t stream);

@@ -767,3 +767,49 @@ def test_gemm_with_the_clamped_gate_in_its_epilogue(T, F, K):
     plan.run(out, T, Cb.GEMM_SWIGLU_BF16)
     torch.cuda.synchronize()
     assert torch.allclose(out[:, :F].cpu().double(), xg * torch.sigmoid(xg) * xu, atol=3e-2, rtol=1e-2)
+
+
+@pytest.mark.parametrize("H,D,V", [(2, 64, 128), (1, 32, 40), (3, 96, 130), (1, 128, 16)])
+def test_chunked_per_channel_recurrence_against_the_sum_over_pairs(H, D, V):
+    """The tensor-core form for prompt portions: portions that are not multiples of the chunk, a sequence that starts on the
+    token-by-token kernel and goes on in chunks from the same slot, channels that barely decay beside channels that lose
+    everything within a few tokens (their exponents must neither overflow nor spoil their neighbours)."""
+    L, _ = lib()
+    assert L.atx_gated_linear_recurrence_chunked_supported(D) and not L.atx_gated_linear_recurrence_chunked_supported(40)
+    g = torch.Generator().manual_seed(D + V)
+    bf = lambda t: t.to(torch.bfloat16).float()
+    n = {"a": 150, "b": 37}
+    data, want, qs = {}, {}, 0.25
+    for k_, nn in n.items():
+        q, k = bf(torch.randn(nn, H * D, generator=g)), bf(torch.randn(nn, H * D, generator=g))
+        v = bf(torch.randn(nn, H * V, generator=g))
+        ld = -torch.rand(nn, H * D, generator=g).float() * torch.tensor([0.001, 0.3, 40.0])[torch.arange(H * D) % 3]
+        data[k_] = (q, k, v, ld)
+        want[k_] = torch.cat([R.decayed_outer_closed_form(q[:, h * D:(h + 1) * D].double() * qs, k[:, h * D:(h + 1) * D].double(),
+                                                          v[:, h * V:(h + 1) * V].double(), ld[:, h * D:(h + 1) * D].double().exp())
+                              for h in range(H)], 1)
+    state = torch.full((3, H, D, V), 55.0, dtype=torch.float32, device=DEV)
+    at, got = {"a": 0, "b": 0}, {"a": [], "b": []}
+    # (rows of a, rows of b, kernel): b starts token by token, then both go on in chunks
+    for na, nb, chunked in [(33, 3, True), (1, 2, False), (16, 31, True), (100, 1, True)]:
+        live = [(k_, c, s) for k_, c, s in (("b", nb, 0), ("a", na, 2)) if c > 0 and at[k_] < n[k_]]
+        rows = [torch.cat([data[k_][j][at[k_]:at[k_] + c] for k_, c, _ in live]) for j in range(4)]
+        _, starts, cnt, pos0, slots = seq_view([c for _, c, _ in live], [at[k_] for k_, _, _ in live], [s for *_, s in live])
+        qd, kd, vd, ldd = (dev(t) for t in rows)
+        y = torch.zeros(rows[0].shape[0], H * V, dtype=torch.float32, device=DEV)
+        fn = L.atx_gated_linear_recurrence_chunked if chunked else L.atx_gated_linear_recurrence
+        ck(fn(qd.data_ptr(), H * D, kd.data_ptr(), H * D, vd.data_ptr(), H * V, ldd.data_ptr(), H * D, H, D, V, qs, state.data_ptr(),
+              y.data_ptr(), H * V, starts.data_ptr(), cnt.data_ptr(), pos0.data_ptr(), slots.data_ptr(), len(live), 0, stream()))
+        torch.cuda.synchronize()
+        o = 0
+        for k_, c, _ in live:
+            got[k_].append(y[o:o + c].double().cpu())
+            o += c
+            at[k_] += c
+    for k_ in n:
+        res = torch.cat(got[k_])
+        assert res.shape == want[k_].shape and bool(torch.isfinite(res).all())
+        # bf16 operands (pair weights, state read-out as high part + remainder): errors of a few parts in a thousand of the
+        # row's size, not of every element
+        err = (res - want[k_]).abs().amax(-1) / want[k_].abs().amax(-1)
+        assert float(err.max()) < 0.02, (k_, float(err.max()))
