@@ -50,7 +50,7 @@ from .common import _Linear, _use_tc, rotation_table_scaled, stretched_frequenci
 MIXERS = ("gla", "latent_attention", "latent_attention_2")
 GLU_ALPHA = 1.702      # the dense feed-forward's gate is g * sigmoid(GLU_ALPHA * g) ...
 GLU_SHIFT = 1.0        # ... times (up + GLU_SHIFT)
-DEFAULT_DECAY_RANK = 16
+DEFAULT_DECAY_RANK = 32
 
 # ---- configuration --------------------------------------------------------------------------------------------------
 
@@ -257,7 +257,7 @@ def named_shape(name: str) -> Optional[Config]:
     hd = 128 if W >= 4096 else 64
     heads = W // hd
     Fe = max(64, F // 4 // 64 * 64)
-    gla = {"dim": 64, "heads": heads, "vdim": hd, "tau": 16.0, "decay_rank": 16}
+    gla = {"dim": 64, "heads": heads, "vdim": hd, "tau": 8.0, "decay_rank": 32}
     lat2 = {"dim": hd, "heads": heads, "vdim": hd, "kv_rank": 128, "scale": hd ** -0.5, "mask": {"size": 2048}}
     lat = {"dim": hd, "heads": heads, "vdim": hd, "kv_rank": 128, "q_rank": W * 3 // 8, "rot_dim": 64,
            "scale": (hd + 64) ** -0.5,

@@ -260,7 +260,7 @@ def checkpoint_shapes(cfg: dict) -> Dict[str, Tuple[int, ...]]:
             out[p + "canon1"] = (W, taps)
         H, D, V = int(c["heads"]), int(c["dim"]), int(c["vdim"])
         if l["type"] == "gla":
-            rk = int(c.get("decay_rank", 16))
+            rk = int(c.get("decay_rank", 32))
             out.update({m + "q": (H * D, W), m + "k": (H * D, W), m + "v": (H * V, W), m + "g": (H * V, W),
                         m + "o": (W, H * V), m + "norm": (V,), m + "a1": (rk, W), m + "a2": (H * D, rk),
                         m + "a2.b": (H * D,)})

@@ -288,7 +288,7 @@ def test_mixed_batches_equal_each_request_alone(dtype):
 
 def tc_model(experts=True):
     """Sizes that take the tensor-core kernels in bf16: GEMM blocks of 64, latents of 64 and 72 + 24, the chunked recurrence."""
-    return model_cfg([gla(heads=2, dim=64, vdim=64, tau=16.0, rank=16, mlp=dense(128, 2.0)),
+    return model_cfg([gla(heads=2, dim=64, vdim=64, tau=12.0, rank=24, mlp=dense(128, 2.0)),
                       lat2(heads=4, dim=64, vdim=48, rank=64, size=70, scale=0.125, mlp=moe(4, 2, 64, 64) if experts else dense(64, 3.0)),
                       lat2(heads=6, dim=32, vdim=48, rank=64, size=100, scale=0.15, kv_from=1),
                       lat(heads=4, dim=64, vdim=32, rank=72, q_rank=64, rot_dim=24, scale=0.1, mlp=dense(64, 1.0)),
@@ -733,12 +733,12 @@ def test_clamped_gate_norm_per_head_plain_stream_rows_and_renormalised_routing(d
     # routing: the chosen scores divided by their sum, times the scale
     z = torch.randn(9, 12, generator=g).float()
     sel, wgt, zd = torch.zeros(9, 4, dtype=torch.int32, device=DEV), torch.zeros(9, 4, dtype=torch.float32, device=DEV), dev(z)
-    ck(L.atx_moe_route_opts(zd.data_ptr(), 12, None, 11, 4, 2.5, 1, sel.data_ptr(), wgt.data_ptr(), 9, 0, stream()))
+    ck(L.atx_moe_route_opts(zd.data_ptr(), 12, None, 11, 4, 1.75, 1, sel.data_ptr(), wgt.data_ptr(), 9, 0, stream()))
     torch.cuda.synchronize()
     s = torch.softmax(z[:, :11].double(), -1)
     val, idx = s.topk(4, -1)
     assert torch.equal(sel.cpu().long(), idx)
-    assert float((wgt.double().cpu() - val / val.sum(-1, keepdim=True) * 2.5).abs().max()) < 1e-6
+    assert float((wgt.double().cpu() - val / val.sum(-1, keepdim=True) * 1.75).abs().max()) < 1e-6
 
 
 @pytest.mark.parametrize("T,F,K", [(5, 128, 512), (64, 192, 1024), (100, 384, 128), (300, 512, 320)])

@@ -98,7 +98,7 @@ def test_weights_are_stacked_the_way_the_kernels_read_them():
     m = napuzen.Config.from_json(cfg)
     w = napuzen.Weights.from_state_dict(m, wt, torch.device("cpu"), torch.float32)
     l0, l1, l2, l3 = w.layers
-    assert l0.w_in.shape == (18 + 18 + 30 + 30 + 16, 64) and torch.equal(l0.w_in[36:66].double(), wt["l0.mix.v"])
+    assert l0.w_in.shape == (18 + 18 + 30 + 30 + 32, 64) and torch.equal(l0.w_in[36:66].double(), wt["l0.mix.v"])
     assert torch.equal(l0.w_in[96:].double(), wt["l0.mix.a1"])
     assert l1.w_in.shape == (32 + 4 + 20, 64) and torch.equal(l1.w_in[32:36].double(), wt["l1.mix.g"])
     assert l3.w_in.shape == (60 + 6, 64) and l3.dkv_norm is None
@@ -198,9 +198,9 @@ def test_reference_clamps_routing_and_absorbed_latent_attention():
     gg, vv = (3 * u).clamp(max=1.0), (-3 * u).clamp(-1.0, 1.0)
     assert torch.allclose(y, gg * torch.sigmoid(1.702 * gg) * (vv + 1.0)) and bool((y[3 * u > 1.0] >= 0).all())
     router = torch.randn(5, 8, generator=g, dtype=F64)
-    idx, w = R.route(u, router, 2, 2.5)
+    idx, w = R.route(u, router, 2, 1.75)
     s = torch.softmax(u @ router.T, -1)
-    assert torch.allclose(w.sum(-1), torch.full((6,), 2.5, dtype=F64)) and torch.equal(idx, s.topk(2, -1).indices)
+    assert torch.allclose(w.sum(-1), torch.full((6,), 1.75, dtype=F64)) and torch.equal(idx, s.topk(2, -1).indices)
     assert torch.allclose(w[:, 0] / w[:, 1], s.gather(1, idx)[:, 0] / s.gather(1, idx)[:, 1])
     # absorbed form: (W_uk^T q) . c and W_uv (sum_j p_j c_j) equal keys and values written out per head
     cfg = small_cfg()
