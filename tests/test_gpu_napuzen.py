@@ -813,3 +813,54 @@ def test_chunked_per_channel_recurrence_against_the_sum_over_pairs(H, D, V):
         # row's size, not of every element
         err = (res - want[k_]).abs().amax(-1) / want[k_].abs().amax(-1)
         assert float(err.max()) < 0.02, (k_, float(err.max()))
+
+
+def write_checkpoint(folder, cfg, wt):
+    """config.json + model.safetensors (bf16): an 8-byte length, a JSON header of name -> dtype, shape, offsets, then the data."""
+    import json
+    import struct
+
+    cfg = json.loads(json.dumps(cfg))
+    for l in cfg["layers"]:          # what only the tensors' shapes give is not written into config.json
+        l["mixer"].pop("decay_rank", None)
+    (folder / "config.json").write_text(json.dumps(cfg))
+    header, blobs, at = {}, [], 0
+    for name, t in wt.items():
+        raw = t.to(torch.bfloat16).contiguous().view(torch.int16).numpy().tobytes()
+        header[name] = {"dtype": "BF16", "shape": list(t.shape), "data_offsets": [at, at + len(raw)]}
+        blobs.append(raw)
+        at += len(raw)
+    hb = json.dumps(header).encode()
+    (folder / "model.safetensors").write_bytes(struct.pack("<Q", len(hb)) + hb + b"".join(blobs))
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_the_replay_command_reads_a_checkpoint_folder_and_writes_the_logits_asked_for(tmp_path, dtype):
+    import json
+    import os
+    import subprocess
+    import sys
+
+    cfg = model_cfg([lat2(mlp=dense()), gla(rank=7, mlp=moe(6, 2, 16, 24, 1.5)), lat(), lat2(kv_from=0, heads=2, size=30)], width=64,
+                    vocab=80, taps=3)
+    wt = R.random_checkpoint(cfg, 31)
+    write_checkpoint(tmp_path, cfg, wt)
+    reqs = {"a": tokens(50, 80, seed=1), "b": tokens(21, 80, seed=2), "c": tokens(70, 80, seed=3)}
+    steps = [{"step": 0, "entries": [{"id": "a", "tokens": reqs["a"][:30], "want": [0, 29]}, {"id": "b", "tokens": reqs["b"][:20], "want": []}], "end": []},
+             {"step": 1, "entries": [{"id": "a", "tokens": reqs["a"][30:31], "want": [0]}, {"id": "b", "tokens": reqs["b"][20:], "want": [0]}], "end": ["b"]},
+             {"step": 2, "entries": [{"id": "c", "tokens": reqs["c"][:64], "want": [5, 63]}], "end": []},       # a sits this step out
+             {"step": 3, "entries": [{"id": "a", "tokens": reqs["a"][31:], "want": [18]}, {"id": "c", "tokens": reqs["c"][64:], "want": [0, 5]}],
+              "end": ["a", "c"]}]
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    out = tmp_path / "out"
+    p = subprocess.run([sys.executable, os.path.join(root, "bin", "trace_run"), "--model", str(tmp_path), "--dtype", dtype, "--out", str(out),
+                        "--max-tokens", "192"], input="\n".join(json.dumps(s) for s in steps) + "\n", capture_output=True, text=True,
+                       timeout=600)
+    assert p.returncode == 0, p.stderr[-2000:]
+    assert [l for l in p.stdout.splitlines() if l.startswith("done")] == [f"done {i}" for i in range(4)]
+    full = {k: R.forward(cfg, wt, v) for k, v in reqs.items()}
+    want = {0: full["a"][[0, 29]], 1: torch.stack([full["a"][30], full["b"][20]]), 2: full["c"][[5, 63]],
+            3: torch.stack([full["a"][49], full["c"][64], full["c"][69]])}
+    for i, w in want.items():
+        got = np.fromfile(out / f"{i}.f32", dtype="<f4").reshape(-1, 80)
+        assert got.shape == tuple(w.shape) and close(got, w, dtype, cfg), (i, dtype, rel(got, w))
