@@ -669,7 +669,7 @@ conv_residual_long_kernel(const float* __restrict__ x, long long ld, const XT* _
 // ---- data-dependent decay per channel through a low-rank projection -------------------------------------------------
 // z[t, c] = b[c] + sum_r A[c, r] * lo[t, r];  out[t, c] = log(sigmoid(z)^(1/tau)) = -softplus(-z) / tau  (fp32, <= 0).
 // lo: the fp32 output of the first (narrow) projection, R columns at pitch ld. One CTA per row tile of 8 rows; the narrow
-// rows sit in shared memory and a thread owns a channel (its R weights in registers when R <= 32).
+// rows sit in shared memory and a thread owns a channel, walking its R weights once for the tile's eight rows.
 template <typename XT>
 __global__ void __launch_bounds__(256)
 lowrank_logdecay_kernel(const float* __restrict__ lo, long long ld, const XT* __restrict__ A, const XT* __restrict__ b,
